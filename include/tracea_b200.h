@@ -1,0 +1,142 @@
+/* tracea_b200.h -- C ABI of the B200-native Conv2d library (libtracea_b200.so).
+ *
+ * The library is a drop-in for the Conv2d entry of Tracea's FFI: every type below has the layout of
+ * the reference's `#[repr(C)]` / C declaration of the same name, and `tracea_conv2d` has the
+ * reference's six-argument signature, so a caller built against the reference's own
+ * `include/tracea.hpp` links against this library unchanged. Each declaration cites the reference
+ * interface it replaces (paths are relative to the reference project's root).
+ *
+ * Plain C: pointers and sizes only, no C++ or torch types.
+ */
+#ifndef TRACEA_B200_H_
+#define TRACEA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes: include/tracea.hpp:16-23, tracea-ffi/src/lib.rs:23-30. */
+typedef enum {
+  TRACEA_SUCCESS = 0,
+  TRACEA_INVALID_PARAMS = 1,
+  TRACEA_UNSUPPORTED_CONFIG = 2,
+  TRACEA_CUDA_ERROR = 3,
+  TRACEA_CPU_ERROR = 4,
+  TRACEA_UNKNOWN_ERROR = 99
+} TraceaStatus;
+
+/* Element types: include/tracea.hpp:29-35, tracea-ffi/src/lib.rs:34-40.
+ * This library computes FLOAT32 (as TF32 on the tensor cores), FLOAT16 and BFLOAT16, all with
+ * fp32 accumulation. INT32 / INT8 are rejected with TRACEA_UNSUPPORTED_CONFIG. */
+typedef enum {
+  TRACEA_DTYPE_FLOAT32 = 0,
+  TRACEA_DTYPE_FLOAT16 = 1,
+  TRACEA_DTYPE_BFLOAT16 = 2,
+  TRACEA_DTYPE_INT32 = 3,
+  TRACEA_DTYPE_INT8 = 4
+} TraceaDType;
+
+/* Fused epilogue selector: include/tracea.hpp:37-47; op lists per kind follow
+ * src/interface/c_bindings.rs:144-197 (bias is added only under the BIAS_* kinds and only if `b`
+ * is non-NULL; residual only under the RESIDUAL* kinds and only if non-NULL).
+ * Values 9 and 10 extend the enum: the reference's runtime entry accepts the op string
+ * "bias+residual+relu" (src/interface/python.rs:41-87) but its C enum has no value for it.
+ * Order is always bias -> residual -> activation. */
+typedef enum {
+  TRACEA_EPILOGUE_IDENTITY = 0,
+  TRACEA_EPILOGUE_BIAS_ADD = 1,
+  TRACEA_EPILOGUE_RELU = 2,
+  TRACEA_EPILOGUE_GELU = 3,
+  TRACEA_EPILOGUE_SILU = 4,
+  TRACEA_EPILOGUE_BIAS_RELU = 5,
+  TRACEA_EPILOGUE_BIAS_SILU = 6,
+  TRACEA_EPILOGUE_RESIDUAL = 7,
+  TRACEA_EPILOGUE_RESIDUAL_RELU = 8,
+  TRACEA_EPILOGUE_BIAS_RESIDUAL_RELU = 9,
+  TRACEA_EPILOGUE_BIAS_RESIDUAL = 10
+} TraceaEpilogueKind;
+
+/* Borrowed tensor view: include/tracea.hpp:59-66, tracea-ffi/src/lib.rs:42-57.
+ * `shape` is always the logical shape (x: N,C,H,W; w: K,C,R,S; out: N,K,Ho,Wo; bias: K);
+ * `stride` is in elements and decides the physical layout. Channels-last memory
+ * (stride[1] == 1) is consumed and produced directly; NCHW-contiguous x / OIHW-contiguous w go
+ * through a transpose into library scratch first. `device_id` -1 means host memory: the
+ * library stages such tensors through the current CUDA device and synchronises before returning. */
+typedef struct {
+  void *ptr;
+  uint32_t rank;
+  const uint64_t *shape;
+  const int64_t *stride;
+  TraceaDType dtype;
+  int32_t device_id;
+} TraceaTensorView;
+
+/* Conv2d parameters: include/tracea.hpp:72-82 (the tracea-ffi crate's struct,
+ * tracea-ffi/src/lib.rs:61-71, is the same minus `epilogue`). */
+typedef struct {
+  uint32_t stride_h;
+  uint32_t stride_w;
+  uint32_t padding_h;
+  uint32_t padding_w;
+  uint32_t dilation_h;
+  uint32_t dilation_w;
+  uint32_t groups;
+  TraceaEpilogueKind epilogue;
+  void *stream; /* cudaStream_t; NULL = default stream. Work is enqueued, not synchronised. */
+} TraceaConv2dParams;
+
+/* The older parameter block without `epilogue` (tracea-ffi/src/lib.rs:61-71). */
+typedef struct {
+  uint32_t stride_h;
+  uint32_t stride_w;
+  uint32_t padding_h;
+  uint32_t padding_w;
+  uint32_t dilation_h;
+  uint32_t dilation_w;
+  uint32_t groups;
+  void *stream;
+} TraceaConv2dParamsV0;
+
+/* out = epilogue(conv2d(x, w)). Replaces include/tracea.hpp:107-110 and the in-crate entry
+ * src/interface/c_bindings.rs:205-290. Validation mirrors tracea-ffi/src/lib.rs:150-207:
+ * NULL x.ptr / w.ptr / out -> INVALID_PARAMS; rank != 4 -> INVALID_PARAMS; groups != 1 ->
+ * UNSUPPORTED_CONFIG; zero stride or an `out` shape that is not [N,K,Ho,Wo] -> INVALID_PARAMS. */
+TraceaStatus tracea_conv2d(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView *b,
+                           const TraceaTensorView *residual, TraceaTensorView *out,
+                           TraceaConv2dParams params);
+
+/* Five-argument form of the tracea-ffi crate (tracea-ffi/src/lib.rs:121-128): no residual, no
+ * epilogue field; bias is added when `b` is non-NULL. Same symbol name as the six-argument form
+ * in the reference, so it is exported here under a suffix. */
+TraceaStatus tracea_conv2d_v0(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView *b,
+                              TraceaTensorView *out, TraceaConv2dParamsV0 params);
+
+/* Thread-local last error text: tracea-ffi/src/lib.rs:87-109. Returns bytes copied (without the
+ * terminating NUL), -1 when buf is NULL or len is 0. */
+int32_t tracea_get_last_error(uint8_t *buf, size_t len);
+void tracea_clear_error(void);
+
+/* Version 0.1.0, as tracea-ffi/src/lib.rs:244-251. */
+uint32_t tracea_version_major(void);
+uint32_t tracea_version_minor(void);
+uint32_t tracea_version_patch(void);
+
+/* Optional, idempotent runtime bring-up / tear-down (include/tracea.h:26-31,
+ * src/interface/c_bindings.rs:103-119). tracea_conv2d initialises lazily, so neither is required.
+ * tracea_init returns 0 on success, -1 if no CUDA device can be opened. */
+int tracea_init(void);
+void tracea_shutdown(void);
+
+/* Reads and clears the device-side status word of `device_id`: 0 when every conv kernel launched
+ * so far on that device finished normally, otherwise the code of the first bounded wait that ran
+ * out inside a kernel (see conv2d_sm100.cuh). Call after synchronising the stream. The reference
+ * has no counterpart: its kernels spin without limit. */
+uint32_t tracea_b200_device_status(int32_t device_id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRACEA_B200_H_ */

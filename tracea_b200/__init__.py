@@ -1,0 +1,13 @@
+"""tracea_b200: a B200 (sm_100a) implicit-GEMM Conv2d behind Tracea's operator surface.
+
+Layers, bottom up:
+  csrc/            hand-written CUDA (TMA im2col -> tcgen05.mma -> TMEM -> fused epilogue) + the C ABI
+  ffi              ctypes binding of that C ABI (include/tracea_b200.h)
+  ops              the reference's Python operator surface (tracea.ops.conv2d, Context.conv2d) on torch tensors
+
+Importing the package does not load the compiled library; the first call does, and raises if the
+library has not been built. There is no fallback implementation.
+"""
+from . import ffi  # noqa: F401
+
+__version__ = "0.1.0"

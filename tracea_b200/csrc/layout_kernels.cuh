@@ -1,0 +1,64 @@
+// Layout adapters for callers that hand over NCHW-contiguous activations or OIHW-contiguous
+// weights (the layouts include/tracea.hpp:101-105 documents). The conv kernel itself reads
+// channels-last memory, which is what the reference's kernel reads too (NHWC input, conv.rs:202-247).
+// Both adapters read through arbitrary element strides and write dense, channel-padded buffers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tb200 {
+
+// x[n, c, h, w] (element strides sn, sc, sh, sw) -> dst[n][h*W + w][Cp] with channels c >= C
+// zero-filled. One CTA moves a 32 (channels) x 32 (pixels) tile through shared memory so that
+// both sides are coalesced when the source is NCHW-contiguous.
+template <typename T>
+__global__ void to_channels_last_kernel(const T* __restrict__ src, T* __restrict__ dst, int C, int H,
+                                        int W, int Cp, long long sn, long long sc, long long sh,
+                                        long long sw) {
+  __shared__ T tile[32][33];
+  const int HW = H * W;
+  const int n = blockIdx.z;
+  const int p0 = blockIdx.x * 32;
+  const int c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x;  // 0..31
+  const int ty = threadIdx.y;  // 0..7
+  // read: consecutive tx -> consecutive pixels (contiguous for NCHW sources)
+  const int p = p0 + tx;
+  long long poff = 0;
+  if (p < HW) {
+    const int h = p / W;
+    poff = h * sh + (p - h * W) * sw;
+  }
+  for (int i = ty; i < 32; i += 8) {
+    const int c = c0 + i;
+    T v = T(0);
+    if (p < HW && c < C) v = src[n * sn + c * sc + poff];
+    tile[i][tx] = v;
+  }
+  __syncthreads();
+  // write: consecutive tx -> consecutive channels
+  const int c = c0 + tx;
+  for (int i = ty; i < 32; i += 8) {
+    const int pp = p0 + i;
+    if (pp < HW && c < Cp) dst[(static_cast<long long>(n) * HW + pp) * Cp + c] = tile[tx][i];
+  }
+}
+
+// w[k, c, r, s] (element strides) -> dst[k][r][s][Cp], zero-padded channels: the K-major B operand
+// whose Kgemm axis runs (r, s, c), the order the reference walks it (conv.rs:209-210).
+template <typename T>
+__global__ void pack_weights_krsc_kernel(const T* __restrict__ src, T* __restrict__ dst,
+                                         long long total, int C, int R, int S, int Cp, long long sk,
+                                         long long sc, long long sr, long long ss) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= total) return;
+  const int c = static_cast<int>(i % Cp);
+  long long t = i / Cp;
+  const int s = static_cast<int>(t % S);
+  t /= S;
+  const int r = static_cast<int>(t % R);
+  const long long k = t / R;
+  dst[i] = (c < C) ? src[k * sk + c * sc + r * sr + s * ss] : T(0);
+}
+
+}  // namespace tb200

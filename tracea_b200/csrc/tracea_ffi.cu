@@ -1,0 +1,805 @@
+// Host side of libtracea_b200.so: the C ABI of include/tracea_b200.h on top of the sm_100a conv
+// kernel. It takes the place of three pieces of the reference for this one path: the FFI shim
+// (tracea-ffi/src/lib.rs:121-238, whose CUDA body is a stub), the NVRTC code emitter + compile
+// cache (src/emitter/cuda/conv.rs, src/runtime/manager/kernel.rs:123-327) and the tile-config
+// search (src/policy/standard.rs:73-113) -- kernels are compiled ahead of time and the tile
+// width is picked by a closed-form cost rule.
+//
+// There is no CPU compute path in this library: every call ends in a kernel launch on a CUDA
+// device or in an error status.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <exception>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/tracea_b200.h"
+#include "conv2d_sm100.cuh"
+#include "layout_kernels.cuh"
+
+namespace {
+
+using tb200::ConvKernelArgs;
+
+// ------------------------------------------------------------------ last error (thread local)
+thread_local std::string g_last_error;
+
+void set_error(const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+}
+
+struct StatusError {
+  TraceaStatus status;
+};
+
+#define TB_FAIL(status_, ...)        \
+  do {                               \
+    set_error(__VA_ARGS__);          \
+    throw StatusError{status_};      \
+  } while (0)
+
+#define TB_CUDA(expr)                                                                   \
+  do {                                                                                  \
+    cudaError_t e_ = (expr);                                                            \
+    if (e_ != cudaSuccess) {                                                            \
+      TB_FAIL(TRACEA_CUDA_ERROR, "%s failed: %s", #expr, cudaGetErrorString(e_));       \
+    }                                                                                   \
+  } while (0)
+
+// ------------------------------------------------------------------ driver entry points
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  int num_sms = 0;
+  cudaMemPool_t pool = nullptr;
+  uint32_t* status = nullptr;  // pinned, mapped: kernels write error codes the host reads directly
+  bool attr_set[3][3] = {};    // [dtype][bn index]
+};
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mutex;
+DeviceState g_dev[kMaxDevices];
+EncodeTiledFn g_encode_tiled = nullptr;
+EncodeIm2colFn g_encode_im2col = nullptr;
+
+void load_driver_entry_points() {
+  if (g_encode_tiled != nullptr && g_encode_im2col != nullptr) return;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  TB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+  if (fn == nullptr || qres != cudaDriverEntryPointSuccess)
+    TB_FAIL(TRACEA_CUDA_ERROR, "driver does not export cuTensorMapEncodeTiled");
+  g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  fn = nullptr;
+  TB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres));
+  if (fn == nullptr || qres != cudaDriverEntryPointSuccess)
+    TB_FAIL(TRACEA_CUDA_ERROR, "driver does not export cuTensorMapEncodeIm2col");
+  g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+}
+
+// Brings up the per-device state (with `dev` current). Called under g_mutex.
+DeviceState& device_state(int dev) {
+  if (dev < 0 || dev >= kMaxDevices) TB_FAIL(TRACEA_INVALID_PARAMS, "device_id %d out of range", dev);
+  DeviceState& st = g_dev[dev];
+  if (st.ready) return st;
+  cudaDeviceProp prop;
+  TB_CUDA(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major != 10)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG,
+            "device %d is sm_%d%d; this library only carries sm_100a kernels", dev, prop.major,
+            prop.minor);
+  st.num_sms = prop.multiProcessorCount;
+  load_driver_entry_points();
+  cudaMemPoolProps pp = {};
+  pp.allocType = cudaMemAllocationTypePinned;
+  pp.handleTypes = cudaMemHandleTypeNone;
+  pp.location.type = cudaMemLocationTypeDevice;
+  pp.location.id = dev;
+  TB_CUDA(cudaMemPoolCreate(&st.pool, &pp));
+  uint64_t keep = ~0ull;  // keep freed scratch cached in the pool instead of returning it to the OS
+  TB_CUDA(cudaMemPoolSetAttribute(st.pool, cudaMemPoolAttrReleaseThreshold, &keep));
+  TB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&st.status), 4 * sizeof(uint32_t),
+                        cudaHostAllocMapped | cudaHostAllocPortable));
+  memset(st.status, 0, 4 * sizeof(uint32_t));
+  st.ready = true;
+  return st;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  explicit DeviceGuard(int dev) {
+    TB_CUDA(cudaGetDevice(&prev));
+    if (prev != dev) {
+      TB_CUDA(cudaSetDevice(dev));
+      switched = true;
+    }
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+// Stream-ordered scratch from the library's pool; released (stream-ordered) by the destructor.
+struct Scratch {
+  void* ptr = nullptr;
+  cudaStream_t stream = nullptr;
+  Scratch() = default;
+  Scratch(const Scratch&) = delete;
+  Scratch& operator=(const Scratch&) = delete;
+  void alloc(DeviceState& st, size_t bytes, cudaStream_t s) {
+    stream = s;
+    TB_CUDA(cudaMallocFromPoolAsync(&ptr, bytes == 0 ? 16 : bytes, st.pool, s));
+  }
+  ~Scratch() {
+    if (ptr != nullptr) cudaFreeAsync(ptr, stream);
+  }
+};
+
+// ------------------------------------------------------------------ views
+struct View4 {
+  void* ptr = nullptr;
+  long long shape[4] = {0, 0, 0, 0};
+  long long stride[4] = {0, 0, 0, 0};
+  TraceaDType dtype = TRACEA_DTYPE_FLOAT32;
+  int device = -1;
+};
+
+int elem_size(TraceaDType t) {
+  switch (t) {
+    case TRACEA_DTYPE_FLOAT32: return 4;
+    case TRACEA_DTYPE_FLOAT16: return 2;
+    case TRACEA_DTYPE_BFLOAT16: return 2;
+    default: return 0;
+  }
+}
+
+const char* dtype_name(TraceaDType t) {
+  switch (t) {
+    case TRACEA_DTYPE_FLOAT32: return "float32";
+    case TRACEA_DTYPE_FLOAT16: return "float16";
+    case TRACEA_DTYPE_BFLOAT16: return "bfloat16";
+    case TRACEA_DTYPE_INT32: return "int32";
+    case TRACEA_DTYPE_INT8: return "int8";
+    default: return "?";
+  }
+}
+
+View4 load_view4(const TraceaTensorView& v, const char* name) {
+  if (v.rank != 4) TB_FAIL(TRACEA_INVALID_PARAMS, "Expected 4D tensors (NCHW): %s has rank %u", name, v.rank);
+  if (v.shape == nullptr) TB_FAIL(TRACEA_INVALID_PARAMS, "%s: shape array is NULL", name);
+  View4 o;
+  o.ptr = v.ptr;
+  o.dtype = v.dtype;
+  o.device = v.device_id;
+  for (int i = 0; i < 4; ++i) {
+    o.shape[i] = static_cast<long long>(v.shape[i]);
+    if (o.shape[i] <= 0 || o.shape[i] > 0x7fffffffLL)
+      TB_FAIL(TRACEA_INVALID_PARAMS, "%s: shape[%d] = %llu is out of range", name, i,
+              (unsigned long long)v.shape[i]);
+  }
+  if (v.stride != nullptr) {
+    for (int i = 0; i < 4; ++i) o.stride[i] = v.stride[i];
+  } else {  // contiguous row-major, what tracea::TensorView builds (include/tracea.hpp:218-228)
+    long long s = 1;
+    for (int i = 3; i >= 0; --i) {
+      o.stride[i] = s;
+      s *= o.shape[i];
+    }
+  }
+  for (int i = 0; i < 4; ++i)
+    if (o.stride[i] < 0) TB_FAIL(TRACEA_INVALID_PARAMS, "%s: negative stride[%d]", name, i);
+  return o;
+}
+
+// Number of elements from the first to the last addressed element, inclusive.
+long long span_elems(const View4& v) {
+  long long s = 1;
+  for (int i = 0; i < 4; ++i) s += (v.shape[i] - 1) * v.stride[i];
+  return s;
+}
+long long num_elems(const View4& v) { return v.shape[0] * v.shape[1] * v.shape[2] * v.shape[3]; }
+
+// Strides of extent-1 dimensions carry no information (torch reports arbitrary values for them);
+// when the channel axis is innermost, rewrite them to the dense channels-last values so that the
+// layout tests below and the TMA stride rules see a consistent picture.
+void canon_channels_last(View4& v) {
+  if (v.shape[1] != 1 && v.stride[1] != 1) return;
+  if (v.shape[1] == 1) v.stride[1] = 1;
+  if (v.shape[3] == 1) v.stride[3] = v.shape[1];
+  if (v.shape[2] == 1) v.stride[2] = v.shape[3] * v.stride[3];
+  if (v.shape[0] == 1) v.stride[0] = v.shape[2] * v.stride[2];
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ------------------------------------------------------------------ epilogue decoding
+struct Epilogue {
+  bool bias = false;
+  bool residual = false;
+  int act = tb200::kActNone;
+};
+
+// Kind -> op list, after src/interface/c_bindings.rs:144-197.
+Epilogue decode_epilogue(TraceaEpilogueKind kind, bool have_bias, bool have_res) {
+  Epilogue e;
+  switch (kind) {
+    case TRACEA_EPILOGUE_IDENTITY: break;
+    case TRACEA_EPILOGUE_BIAS_ADD: e.bias = have_bias; break;
+    case TRACEA_EPILOGUE_RELU: e.act = tb200::kActRelu; break;
+    case TRACEA_EPILOGUE_GELU: e.act = tb200::kActGelu; break;
+    case TRACEA_EPILOGUE_SILU: e.act = tb200::kActSilu; break;
+    case TRACEA_EPILOGUE_BIAS_RELU: e.bias = have_bias; e.act = tb200::kActRelu; break;
+    case TRACEA_EPILOGUE_BIAS_SILU:
+      // the reference emits the fused BiasAddSiLU functor only when a bias is present
+      e.bias = have_bias;
+      e.act = have_bias ? tb200::kActSilu : tb200::kActNone;
+      break;
+    case TRACEA_EPILOGUE_RESIDUAL: e.residual = have_res; break;
+    case TRACEA_EPILOGUE_RESIDUAL_RELU: e.residual = have_res; e.act = tb200::kActRelu; break;
+    case TRACEA_EPILOGUE_BIAS_RESIDUAL_RELU:
+      e.bias = have_bias; e.residual = have_res; e.act = tb200::kActRelu; break;
+    case TRACEA_EPILOGUE_BIAS_RESIDUAL: e.bias = have_bias; e.residual = have_res; break;
+    default:
+      TB_FAIL(TRACEA_INVALID_PARAMS, "unknown epilogue kind %d", static_cast<int>(kind));
+  }
+  return e;
+}
+
+// ------------------------------------------------------------------ tile selection
+// Relative cost of one 128-byte k-step of a 128 x BN tile on one SM: the larger of the tensor
+// pipe time (BN/2 cycles per MMA) and the shared-memory operand read time
+// ((128 + BN) * 32 B per MMA at 128 B/cycle). The widest tile wins ties: it re-reads A least.
+int pick_bn(long long m_tiles, int k_out, int num_sms) {
+  const int bns[3] = {256, 128, 64};
+  const int step_cost[3] = {512, 256, 192};
+  long long best_cost = -1;
+  int best = 64;
+  for (int i = 0; i < 3; ++i) {
+    const long long n_tiles = (k_out + bns[i] - 1) / bns[i];
+    const long long waves = (m_tiles * n_tiles + num_sms - 1) / num_sms;
+    const long long cost = waves * step_cost[i];
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bns[i];
+    }
+  }
+  return best;
+}
+
+int pick_stages(int bn) {
+  const int stage_bytes = tb200::kBlockM * tb200::kStageKBytes + bn * tb200::kStageKBytes;
+  int s = (232448 - 1536) / stage_bytes;  // 227 KB opt-in limit per CTA
+  return std::min(s, tb200::kMaxStages);
+}
+
+template <typename OutT, int BN>
+void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, const CUtensorMap& tw,
+                const ConvKernelArgs& args, int grid, int smem, cudaStream_t stream) {
+  auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN>;
+  if (!st.attr_set[dt_idx][bn_idx]) {
+    TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    st.attr_set[dt_idx][bn_idx] = true;
+  }
+  kern<<<grid, tb200::kNumThreads, smem, stream>>>(tx, tw, args);
+  TB_CUDA(cudaGetLastError());
+}
+
+template <typename OutT>
+void launch_bn(DeviceState& st, int dt_idx, int bn, const CUtensorMap& tx, const CUtensorMap& tw,
+               const ConvKernelArgs& args, int grid, int smem, cudaStream_t stream) {
+  switch (bn) {
+    case 64: launch_one<OutT, 64>(st, dt_idx, 0, tx, tw, args, grid, smem, stream); break;
+    case 128: launch_one<OutT, 128>(st, dt_idx, 1, tx, tw, args, grid, smem, stream); break;
+    default: launch_one<OutT, 256>(st, dt_idx, 2, tx, tw, args, grid, smem, stream); break;
+  }
+}
+
+CUtensorMapDataType tmap_dtype(TraceaDType t) {
+  switch (t) {
+    case TRACEA_DTYPE_FLOAT16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    case TRACEA_DTYPE_BFLOAT16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    default: return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  }
+}
+
+CUtensorMapSwizzle tmap_swizzle(int chunk_bytes) {
+  switch (chunk_bytes) {
+    case 128: return CU_TENSOR_MAP_SWIZZLE_128B;
+    case 64: return CU_TENSOR_MAP_SWIZZLE_64B;
+    case 32: return CU_TENSOR_MAP_SWIZZLE_32B;
+    default: return CU_TENSOR_MAP_SWIZZLE_NONE;
+  }
+}
+
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v != nullptr && *v != '\0') ? atoi(v) : dflt;
+}
+
+// ------------------------------------------------------------------ the device path
+// All pointers are device pointers on `dev`. x: [N,C,H,W], w: [K,C,R,S], out: [N,K,Ho,Wo] (logical).
+void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* bias,
+                   const View4* residual, const View4& out, const TraceaConv2dParams& p,
+                   const Epilogue& epi) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceGuard guard(dev);
+  DeviceState& st = device_state(dev);
+  cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
+
+  if (st.status[0] != 0u) {
+    const uint32_t code = st.status[0], blk = st.status[1], det = st.status[2];
+    memset(st.status, 0, 4 * sizeof(uint32_t));
+    TB_FAIL(TRACEA_CUDA_ERROR,
+            "an earlier conv kernel on device %d gave up a bounded wait (code %u, block %u, detail %u)",
+            dev, code, blk, det);
+  }
+
+  const int es = elem_size(x_in.dtype);
+  const long long N = x_in.shape[0], C = x_in.shape[1], H = x_in.shape[2], W = x_in.shape[3];
+  const long long K = w_in.shape[0], R = w_in.shape[2], S = w_in.shape[3];
+  const long long Ho = out.shape[2], Wo = out.shape[3];
+  const long long M = N * Ho * Wo;
+  if (M > 0x7fffff00LL) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "N*Ho*Wo = %lld exceeds 2^31", M);
+  if (p.stride_h > 8 || p.stride_w > 8)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "stride > 8 is not supported (TMA traversal stride limit)");
+  if ((S - 1) * p.dilation_w > 255 || (R - 1) * p.dilation_h > 255)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "filter extent > 256 is not supported (TMA im2col offset limit)");
+  if (p.padding_h > 32767 || p.padding_w > 32767)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "padding > 32767 is not supported");
+
+  const int vec_elems = 16 / es;
+  const long long Cp = (C + vec_elems - 1) / vec_elems * vec_elems;
+
+  // ---- activations: consume channels-last memory directly, otherwise transpose into scratch
+  View4 x = x_in;
+  Scratch x_scratch;
+  const bool x_direct = x.stride[1] == 1 && C == Cp && aligned16(x.ptr) &&
+                        (x.stride[3] * es) % 16 == 0 && (x.stride[2] * es) % 16 == 0 &&
+                        (x.stride[0] * es) % 16 == 0 && x.stride[3] >= C;
+  if (!x_direct || env_int("TRACEA_B200_FORCE_STAGING", 0)) {
+    x_scratch.alloc(st, static_cast<size_t>(N * H * W * Cp) * es, stream);
+    dim3 grid(static_cast<unsigned>((H * W + 31) / 32), static_cast<unsigned>((Cp + 31) / 32),
+              static_cast<unsigned>(N));
+    if (grid.y > 65535u || grid.z > 65535u)
+      TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "layout adapter: N or C too large");
+    dim3 block(32, 8);
+    if (es == 2)
+      tb200::to_channels_last_kernel<uint16_t><<<grid, block, 0, stream>>>(
+          static_cast<const uint16_t*>(x.ptr), static_cast<uint16_t*>(x_scratch.ptr), (int)C, (int)H,
+          (int)W, (int)Cp, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
+    else
+      tb200::to_channels_last_kernel<uint32_t><<<grid, block, 0, stream>>>(
+          static_cast<const uint32_t*>(x.ptr), static_cast<uint32_t*>(x_scratch.ptr), (int)C, (int)H,
+          (int)W, (int)Cp, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
+    TB_CUDA(cudaGetLastError());
+    x.ptr = x_scratch.ptr;
+    x.stride[0] = H * W * Cp;
+    x.stride[1] = 1;
+    x.stride[2] = W * Cp;
+    x.stride[3] = Cp;
+  }
+
+  // ---- weights: consume dense [K][R][S][C] memory directly, otherwise repack into scratch
+  const void* w_ptr = w_in.ptr;
+  Scratch w_scratch;
+  const bool w_direct = C == Cp && (w_in.stride[1] == 1) && w_in.stride[3] == C &&
+                        w_in.stride[2] == S * C && w_in.stride[0] == R * S * C && aligned16(w_in.ptr);
+  if (!w_direct) {
+    const long long total = K * R * S * Cp;
+    w_scratch.alloc(st, static_cast<size_t>(total) * es, stream);
+    const int threads = 256;
+    const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+    if (es == 2)
+      tb200::pack_weights_krsc_kernel<uint16_t><<<blocks, threads, 0, stream>>>(
+          static_cast<const uint16_t*>(w_in.ptr), static_cast<uint16_t*>(w_scratch.ptr), total, (int)C,
+          (int)R, (int)S, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
+    else
+      tb200::pack_weights_krsc_kernel<uint32_t><<<blocks, threads, 0, stream>>>(
+          static_cast<const uint32_t*>(w_in.ptr), static_cast<uint32_t*>(w_scratch.ptr), total, (int)C,
+          (int)R, (int)S, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
+    TB_CUDA(cudaGetLastError());
+    w_ptr = w_scratch.ptr;
+  }
+
+  // ---- k-chunking: the widest power-of-two row (<= 128 B) that divides one pixel's channels
+  const long long row_bytes = Cp * es;
+  int chunk_bytes = 16;
+  for (int cb = 128; cb >= 16; cb >>= 1) {
+    if (row_bytes % cb == 0) {
+      chunk_bytes = cb;
+      break;
+    }
+  }
+  const int forced_chunk = env_int("TRACEA_B200_FORCE_CHUNK", 0);
+  if (forced_chunk == 16 || forced_chunk == 32 || forced_chunk == 64 || forced_chunk == 128) {
+    if (row_bytes % forced_chunk == 0) chunk_bytes = forced_chunk;
+  }
+  const int chunk_elems = chunk_bytes / es;
+  const int chunks_per_tap = static_cast<int>(Cp / chunk_elems);
+  const long long total_chunks_ll = R * S * chunks_per_tap;
+  if (total_chunks_ll > 0x7fffffffLL / 128) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "R*S*C too large");
+  const long long Kgemm = R * S * Cp;
+
+  // ---- tiles
+  const long long m_tiles = (M + tb200::kBlockM - 1) / tb200::kBlockM;
+  int bn = pick_bn(m_tiles, static_cast<int>(K), st.num_sms);
+  const int forced_bn = env_int("TRACEA_B200_FORCE_BN", 0);
+  if (forced_bn == 64 || forced_bn == 128 || forced_bn == 256) bn = forced_bn;
+  const long long n_tiles = (K + bn - 1) / bn;
+  if (m_tiles * n_tiles > 0x7fffffffLL) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "too many tiles");
+  int stages = pick_stages(bn);
+  const int forced_stages = env_int("TRACEA_B200_FORCE_STAGES", 0);
+  if (forced_stages >= 2 && forced_stages <= stages) stages = forced_stages;
+  const int smem = tb200::conv_smem_bytes(bn, stages);
+
+  // ---- tensor maps
+  CUtensorMap tmap_x, tmap_w;
+  // A 1x1 / stride-1 / unpadded conv over dense NHWC memory is a plain [M][C] x [C][K] GEMM; the
+  // tiled map is kept as a cross-check of the im2col path (TRACEA_B200_TILED_A=1).
+  const bool a_tiled = env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
+                       p.stride_w == 1 && p.padding_h == 0 && p.padding_w == 0 && x.stride[3] == Cp &&
+                       x.stride[2] == W * Cp && x.stride[0] == H * W * Cp;
+  if (a_tiled) {
+    const cuuint64_t gdim[2] = {(cuuint64_t)Cp, (cuuint64_t)M};
+    const cuuint64_t gstr[1] = {(cuuint64_t)(Cp * es)};
+    const cuuint32_t box[2] = {(cuuint32_t)chunk_elems, (cuuint32_t)tb200::kBlockM};
+    const cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = g_encode_tiled(&tmap_x, tmap_dtype(x.dtype), 2, x.ptr, gdim, gstr, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, tmap_swizzle(chunk_bytes),
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled (A) failed with %d", (int)r);
+  } else {
+    const cuuint64_t gdim[4] = {(cuuint64_t)Cp, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    const cuuint64_t gstr[3] = {(cuuint64_t)(x.stride[3] * es), (cuuint64_t)(x.stride[2] * es),
+                                (cuuint64_t)(x.stride[0] * es)};
+    const int lower[2] = {-(int)p.padding_w, -(int)p.padding_h};
+    const int upper[2] = {(int)p.padding_w - (int)((S - 1) * p.dilation_w),
+                          (int)p.padding_h - (int)((R - 1) * p.dilation_h)};
+    const cuuint32_t estr[4] = {1u, p.stride_w, p.stride_h, 1u};
+    CUresult r = g_encode_im2col(&tmap_x, tmap_dtype(x.dtype), 4, x.ptr, gdim, gstr, lower, upper,
+                                 (cuuint32_t)chunk_elems, (cuuint32_t)tb200::kBlockM, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, tmap_swizzle(chunk_bytes),
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      TB_FAIL(TRACEA_CUDA_ERROR,
+              "cuTensorMapEncodeIm2col failed with %d (C=%lld W=%lld H=%lld N=%lld chunk=%d B lower=(%d,%d) "
+              "upper=(%d,%d) stride=(%u,%u))",
+              (int)r, Cp, W, H, N, chunk_bytes, lower[0], lower[1], upper[0], upper[1], p.stride_w,
+              p.stride_h);
+  }
+  {
+    const cuuint64_t gdim[2] = {(cuuint64_t)Kgemm, (cuuint64_t)K};
+    const cuuint64_t gstr[1] = {(cuuint64_t)(Kgemm * es)};
+    const cuuint32_t box[2] = {(cuuint32_t)chunk_elems, (cuuint32_t)bn};
+    const cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = g_encode_tiled(&tmap_w, tmap_dtype(x.dtype), 2, const_cast<void*>(w_ptr), gdim, gstr,
+                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, tmap_swizzle(chunk_bytes),
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled failed with %d (Kgemm=%lld K=%lld bn=%d)", (int)r,
+              Kgemm, K, bn);
+  }
+
+  // ---- kernel arguments
+  ConvKernelArgs a;
+  memset(&a, 0, sizeof(a));
+  a.M = static_cast<int>(M);
+  a.K_out = static_cast<int>(K);
+  a.Ho = static_cast<int>(Ho);
+  a.Wo = static_cast<int>(Wo);
+  a.stride_h = p.stride_h;
+  a.stride_w = p.stride_w;
+  a.pad_h = p.padding_h;
+  a.pad_w = p.padding_w;
+  a.dil_h = p.dilation_h;
+  a.dil_w = p.dilation_w;
+  a.S = static_cast<int>(S);
+  a.chunk_elems = chunk_elems;
+  a.chunk_bytes = chunk_bytes;
+  a.chunks_per_tap = chunks_per_tap;
+  a.total_chunks = static_cast<int>(total_chunks_ll);
+  a.C = static_cast<int>(Cp);
+  a.a_tiled = a_tiled ? 1 : 0;
+  a.num_m_tiles = static_cast<int>(m_tiles);
+  a.num_n_tiles = static_cast<int>(n_tiles);
+  a.num_stages = stages;
+  const uint32_t fmt = x.dtype == TRACEA_DTYPE_FLOAT16 ? 0u : (x.dtype == TRACEA_DTYPE_BFLOAT16 ? 1u : 2u);
+  a.idesc = tb200::ptx::make_idesc(fmt, tb200::kBlockM, bn);
+  // K-major operand descriptors. Swizzled rows of chunk_bytes: 8-row groups are 8*chunk_bytes apart
+  // (SBO) and one MMA (32 B of K) stays inside a row. Unswizzled 16-byte chunks: an 8-row x 16 B core
+  // matrix is 128 contiguous bytes (SBO) and the MMA's second K half is the next chunk (LBO).
+  const uint32_t a_chunk = tb200::kBlockM * chunk_bytes, b_chunk = bn * chunk_bytes;
+  if (chunk_bytes >= 32) {
+    a.swizzle_mode = chunk_bytes == 128 ? 2u : (chunk_bytes == 64 ? 4u : 6u);
+    a.a_sbo = a.b_sbo = 8u * chunk_bytes;
+    a.a_lbo = a.b_lbo = 0u;
+    const int mma_per_chunk = chunk_bytes / 32;
+    for (int k = 0; k < 4; ++k) {
+      a.a_mma_off[k] = (k / mma_per_chunk) * a_chunk + (k % mma_per_chunk) * 32u;
+      a.b_mma_off[k] = (k / mma_per_chunk) * b_chunk + (k % mma_per_chunk) * 32u;
+    }
+  } else {
+    a.swizzle_mode = 0u;
+    a.a_sbo = a.b_sbo = 128u;
+    a.a_lbo = a_chunk;
+    a.b_lbo = b_chunk;
+    for (int k = 0; k < 4; ++k) {
+      a.a_mma_off[k] = 2u * k * a_chunk;
+      a.b_mma_off[k] = 2u * k * b_chunk;
+    }
+  }
+  a.out = out.ptr;
+  a.out_sn = out.stride[0];
+  a.out_sc = out.stride[1];
+  a.out_sh = out.stride[2];
+  a.out_sw = out.stride[3];
+  auto vec_legal = [&](const View4& v) {
+    return (v.stride[1] == 1) && aligned16(v.ptr) && (v.stride[0] * es) % 16 == 0 &&
+           (v.stride[2] * es) % 16 == 0 && (v.stride[3] * es) % 16 == 0 && (K % vec_elems) == 0;
+  };
+  a.out_vec = vec_legal(out) ? 1 : 0;
+  if (epi.bias && bias != nullptr) {
+    a.bias = bias->ptr;
+    a.bias_is_f32 = bias->dtype == TRACEA_DTYPE_FLOAT32 ? 1 : 0;
+  }
+  if (epi.residual && residual != nullptr) {
+    a.residual = residual->ptr;
+    a.res_sn = residual->stride[0];
+    a.res_sc = residual->stride[1];
+    a.res_sh = residual->stride[2];
+    a.res_sw = residual->stride[3];
+    a.res_vec = vec_legal(*residual) ? 1 : 0;
+  }
+  a.act = epi.act;
+  a.status = st.status;
+
+  const long long tiles = m_tiles * n_tiles;
+  const int grid = static_cast<int>(std::min<long long>(tiles, st.num_sms));
+  switch (x.dtype) {
+    case TRACEA_DTYPE_BFLOAT16:
+      launch_bn<__nv_bfloat16>(st, 0, bn, tmap_x, tmap_w, a, grid, smem, stream);
+      break;
+    case TRACEA_DTYPE_FLOAT16:
+      launch_bn<__half>(st, 1, bn, tmap_x, tmap_w, a, grid, smem, stream);
+      break;
+    default:
+      launch_bn<float>(st, 2, bn, tmap_x, tmap_w, a, grid, smem, stream);
+      break;
+  }
+}
+
+// ------------------------------------------------------------------ host-memory staging
+struct Staged {
+  Scratch buf;
+  View4 view;
+};
+
+void stage_in(DeviceState& st, const View4& host, Staged& s, cudaStream_t stream, bool copy) {
+  const size_t bytes = static_cast<size_t>(span_elems(host)) * elem_size(host.dtype);
+  s.buf.alloc(st, bytes, stream);
+  s.view = host;
+  s.view.ptr = s.buf.ptr;
+  if (copy) TB_CUDA(cudaMemcpyAsync(s.buf.ptr, host.ptr, bytes, cudaMemcpyHostToDevice, stream));
+}
+
+// ------------------------------------------------------------------ validation + dispatch
+void conv2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, const TraceaTensorView* bv,
+                    const TraceaTensorView* rv, TraceaTensorView* ov, const TraceaConv2dParams& p) {
+  if (xv.ptr == nullptr || wv.ptr == nullptr || ov == nullptr || ov->ptr == nullptr)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "Null pointer in input tensors");
+  if (p.groups != 1) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "Unsupported groups: %u", p.groups);
+  if (p.stride_h == 0 || p.stride_w == 0) TB_FAIL(TRACEA_INVALID_PARAMS, "stride must be >= 1");
+  if (p.dilation_h == 0 || p.dilation_w == 0) TB_FAIL(TRACEA_INVALID_PARAMS, "dilation must be >= 1");
+  const int es = elem_size(xv.dtype);
+  if (es == 0)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "Unsupported dtype %s (float32, float16, bfloat16 are supported)",
+            dtype_name(xv.dtype));
+  if (wv.dtype != xv.dtype)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "x is %s but w is %s", dtype_name(xv.dtype), dtype_name(wv.dtype));
+  if (ov->dtype != xv.dtype)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "x is %s but out is %s", dtype_name(xv.dtype), dtype_name(ov->dtype));
+
+  View4 x = load_view4(xv, "x");
+  View4 w = load_view4(wv, "w");
+  View4 out = load_view4(*ov, "out");
+  canon_channels_last(x);
+  canon_channels_last(w);
+  canon_channels_last(out);
+  const long long N = x.shape[0], C = x.shape[1], H = x.shape[2], W = x.shape[3];
+  const long long K = w.shape[0], R = w.shape[2], S = w.shape[3];
+  if (w.shape[1] != C)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "Channel mismatch: x has %lld channels, w has %lld", C, w.shape[1]);
+  const long long eff_h = H + 2LL * p.padding_h - (long long)p.dilation_h * (R - 1) - 1;
+  const long long eff_w = W + 2LL * p.padding_w - (long long)p.dilation_w * (S - 1) - 1;
+  if (eff_h < 0 || eff_w < 0)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "filter %lldx%lld does not fit the padded %lldx%lld input", R, S, H, W);
+  const long long Ho = eff_h / p.stride_h + 1, Wo = eff_w / p.stride_w + 1;
+  if (out.shape[0] != N || out.shape[1] != K || out.shape[2] != Ho || out.shape[3] != Wo)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "out shape [%lld,%lld,%lld,%lld] does not match expected [%lld,%lld,%lld,%lld]",
+            out.shape[0], out.shape[1], out.shape[2], out.shape[3], N, K, Ho, Wo);
+
+  const int dev = x.device;
+  if (w.device != dev || out.device != dev)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "x, w and out must live on the same device");
+
+  View4 bias4, res4;
+  const View4* bias = nullptr;
+  const View4* res = nullptr;
+  if (bv != nullptr) {
+    if (bv->ptr == nullptr) TB_FAIL(TRACEA_INVALID_PARAMS, "bias view has a NULL pointer");
+    if (bv->rank != 1 || bv->shape == nullptr || (long long)bv->shape[0] != K)
+      TB_FAIL(TRACEA_INVALID_PARAMS, "bias must be a rank-1 tensor of length %lld", K);
+    if (bv->stride != nullptr && bv->stride[0] != 1)
+      TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "bias must be contiguous");
+    if (bv->dtype != TRACEA_DTYPE_FLOAT32 && bv->dtype != xv.dtype)
+      TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "bias must be float32 or %s", dtype_name(xv.dtype));
+    if (bv->device_id != dev) TB_FAIL(TRACEA_INVALID_PARAMS, "bias must live on the same device as x");
+    bias4.ptr = bv->ptr;
+    bias4.dtype = bv->dtype;
+    bias4.device = bv->device_id;
+    bias4.shape[0] = K;
+    bias4.shape[1] = bias4.shape[2] = bias4.shape[3] = 1;
+    bias4.stride[0] = 1;
+    bias = &bias4;
+  }
+  if (rv != nullptr) {
+    if (rv->ptr == nullptr) TB_FAIL(TRACEA_INVALID_PARAMS, "residual view has a NULL pointer");
+    res4 = load_view4(*rv, "residual");
+    canon_channels_last(res4);
+    if (res4.dtype != xv.dtype)
+      TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "residual must be %s", dtype_name(xv.dtype));
+    for (int i = 0; i < 4; ++i)
+      if (res4.shape[i] != out.shape[i])
+        TB_FAIL(TRACEA_INVALID_PARAMS, "residual shape must equal the out shape");
+    if (res4.device != dev) TB_FAIL(TRACEA_INVALID_PARAMS, "residual must live on the same device as x");
+    res = &res4;
+  }
+  const Epilogue epi = decode_epilogue(p.epilogue, bias != nullptr, res != nullptr);
+
+  if (dev >= 0) {
+    conv2d_device(dev, x, w, bias, res, out, p, epi);
+    return;
+  }
+
+  // Host memory: stage through the current CUDA device, run the same device path, copy back and
+  // wait, so that the result is in the caller's buffer when the call returns.
+  int cur = 0;
+  TB_CUDA(cudaGetDevice(&cur));
+  cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
+  Staged sx, sw, sb, sr, so;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState& st = device_state(cur);
+    stage_in(st, x, sx, stream, true);
+    stage_in(st, w, sw, stream, true);
+    if (bias != nullptr && epi.bias) stage_in(st, *bias, sb, stream, true);
+    if (res != nullptr && epi.residual) stage_in(st, *res, sr, stream, true);
+    // a strided `out` has gaps the copy back must not clobber: seed the staging buffer with them
+    stage_in(st, out, so, stream, span_elems(out) != num_elems(out));
+  }
+  conv2d_device(cur, sx.view, sw.view, (bias != nullptr && epi.bias) ? &sb.view : nullptr,
+                (res != nullptr && epi.residual) ? &sr.view : nullptr, so.view, p, epi);
+  TB_CUDA(cudaMemcpyAsync(out.ptr, so.buf.ptr, static_cast<size_t>(span_elems(out)) * es,
+                          cudaMemcpyDeviceToHost, stream));
+  TB_CUDA(cudaStreamSynchronize(stream));
+  const uint32_t code = tracea_b200_device_status(cur);
+  if (code != 0u) TB_FAIL(TRACEA_CUDA_ERROR, "conv kernel gave up a bounded wait (code %u)", code);
+}
+
+template <typename F>
+TraceaStatus guarded(const char* what, F&& f) {
+  // mirrors the catch_unwind wrapper of tracea-ffi/src/lib.rs:130-141: nothing escapes the C boundary
+  try {
+    f();
+    return TRACEA_SUCCESS;
+  } catch (const StatusError& e) {
+    return e.status;
+  } catch (const std::exception& e) {
+    set_error("Exception in %s: %s", what, e.what());
+    return TRACEA_UNKNOWN_ERROR;
+  } catch (...) {
+    set_error("Unknown exception in %s", what);
+    return TRACEA_UNKNOWN_ERROR;
+  }
+}
+
+}  // namespace
+
+// ==================================================================== exported C ABI
+extern "C" {
+
+TraceaStatus tracea_conv2d(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView* b,
+                           const TraceaTensorView* residual, TraceaTensorView* out,
+                           TraceaConv2dParams params) {
+  return guarded("tracea_conv2d", [&] { conv2d_checked(x, w, b, residual, out, params); });
+}
+
+TraceaStatus tracea_conv2d_v0(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView* b,
+                              TraceaTensorView* out, TraceaConv2dParamsV0 params) {
+  TraceaConv2dParams p;
+  p.stride_h = params.stride_h;
+  p.stride_w = params.stride_w;
+  p.padding_h = params.padding_h;
+  p.padding_w = params.padding_w;
+  p.dilation_h = params.dilation_h;
+  p.dilation_w = params.dilation_w;
+  p.groups = params.groups;
+  p.epilogue = b != nullptr ? TRACEA_EPILOGUE_BIAS_ADD : TRACEA_EPILOGUE_IDENTITY;
+  p.stream = params.stream;
+  return guarded("tracea_conv2d_v0", [&] { conv2d_checked(x, w, b, nullptr, out, p); });
+}
+
+int32_t tracea_get_last_error(uint8_t* buf, size_t len) {
+  if (buf == nullptr || len == 0) return -1;
+  const size_t n = std::min(g_last_error.size(), len - 1);
+  memcpy(buf, g_last_error.data(), n);
+  buf[n] = 0;
+  return static_cast<int32_t>(n);
+}
+
+void tracea_clear_error(void) { g_last_error.clear(); }
+
+uint32_t tracea_version_major(void) { return 0; }
+uint32_t tracea_version_minor(void) { return 1; }
+uint32_t tracea_version_patch(void) { return 0; }
+
+int tracea_init(void) {
+  const TraceaStatus s = guarded("tracea_init", [&] {
+    int count = 0;
+    TB_CUDA(cudaGetDeviceCount(&count));
+    if (count <= 0) TB_FAIL(TRACEA_CUDA_ERROR, "no CUDA device");
+    int cur = 0;
+    TB_CUDA(cudaGetDevice(&cur));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    device_state(cur);
+  });
+  return s == TRACEA_SUCCESS ? 0 : -1;
+}
+
+void tracea_shutdown(void) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (int d = 0; d < kMaxDevices; ++d) {
+    DeviceState& st = g_dev[d];
+    if (!st.ready) continue;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(d);
+    cudaDeviceSynchronize();
+    if (st.pool != nullptr) cudaMemPoolDestroy(st.pool);
+    if (st.status != nullptr) cudaFreeHost(st.status);
+    st = DeviceState();
+    cudaSetDevice(prev);
+  }
+}
+
+uint32_t tracea_b200_device_status(int32_t device_id) {
+  if (device_id < 0 || device_id >= kMaxDevices) return 0;
+  DeviceState& st = g_dev[device_id];
+  if (!st.ready || st.status == nullptr) return 0;
+  const uint32_t code = st.status[0];
+  if (code != 0u) memset(st.status, 0, 4 * sizeof(uint32_t));
+  return code;
+}
+
+}  // extern "C"

@@ -1,0 +1,137 @@
+"""ctypes binding of the C ABI in include/tracea_b200.h.
+
+The structures repeat the reference's `#[repr(C)]` layouts (tracea-ffi/src/lib.rs:42-71,
+include/tracea.hpp:59-82). Loading fails loudly when the compiled library is absent: there is no
+Python or CPU fallback behind this module.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtracea_b200.so")
+
+# TraceaStatus (include/tracea.hpp:16-23)
+SUCCESS, INVALID_PARAMS, UNSUPPORTED_CONFIG, CUDA_ERROR, CPU_ERROR, UNKNOWN_ERROR = 0, 1, 2, 3, 4, 99
+STATUS_NAMES = {0: "SUCCESS", 1: "INVALID_PARAMS", 2: "UNSUPPORTED_CONFIG", 3: "CUDA_ERROR", 4: "CPU_ERROR",
+                99: "UNKNOWN_ERROR"}
+# TraceaDType (include/tracea.hpp:29-35)
+DTYPE_FLOAT32, DTYPE_FLOAT16, DTYPE_BFLOAT16, DTYPE_INT32, DTYPE_INT8 = 0, 1, 2, 3, 4
+# TraceaEpilogueKind (include/tracea.hpp:37-47) + the two combined kinds this library adds
+(EPILOGUE_IDENTITY, EPILOGUE_BIAS_ADD, EPILOGUE_RELU, EPILOGUE_GELU, EPILOGUE_SILU, EPILOGUE_BIAS_RELU,
+ EPILOGUE_BIAS_SILU, EPILOGUE_RESIDUAL, EPILOGUE_RESIDUAL_RELU, EPILOGUE_BIAS_RESIDUAL_RELU,
+ EPILOGUE_BIAS_RESIDUAL) = range(11)
+
+EXPORTED_SYMBOLS = (
+    "tracea_conv2d", "tracea_conv2d_v0", "tracea_get_last_error", "tracea_clear_error",
+    "tracea_version_major", "tracea_version_minor", "tracea_version_patch", "tracea_init",
+    "tracea_shutdown", "tracea_b200_device_status",
+)
+
+
+class TensorView(ctypes.Structure):
+    _fields_ = [
+        ("ptr", ctypes.c_void_p),
+        ("rank", ctypes.c_uint32),
+        ("shape", ctypes.POINTER(ctypes.c_uint64)),
+        ("stride", ctypes.POINTER(ctypes.c_int64)),
+        ("dtype", ctypes.c_int),
+        ("device_id", ctypes.c_int32),
+    ]
+
+
+class Conv2dParams(ctypes.Structure):
+    _fields_ = [
+        ("stride_h", ctypes.c_uint32), ("stride_w", ctypes.c_uint32),
+        ("padding_h", ctypes.c_uint32), ("padding_w", ctypes.c_uint32),
+        ("dilation_h", ctypes.c_uint32), ("dilation_w", ctypes.c_uint32),
+        ("groups", ctypes.c_uint32),
+        ("epilogue", ctypes.c_int),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+class Conv2dParamsV0(ctypes.Structure):
+    _fields_ = [
+        ("stride_h", ctypes.c_uint32), ("stride_w", ctypes.c_uint32),
+        ("padding_h", ctypes.c_uint32), ("padding_w", ctypes.c_uint32),
+        ("dilation_h", ctypes.c_uint32), ("dilation_w", ctypes.c_uint32),
+        ("groups", ctypes.c_uint32),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+class TraceaError(RuntimeError):
+    """A non-zero TraceaStatus, carrying the library's last-error text."""
+
+    def __init__(self, status, message):
+        super().__init__("tracea_conv2d failed: %s (%s)" % (message, STATUS_NAMES.get(status, status)))
+        self.status = status
+        self.message = message
+
+
+_lib = None
+
+
+def load():
+    """dlopen libtracea_b200.so and declare its prototypes. Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "%s is missing: build it with `python -m tracea_b200.build` (nvcc, sm_100a). "
+            "tracea_b200 has no fallback path." % LIB_PATH)
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.tracea_conv2d.argtypes = [TensorView, TensorView, ctypes.POINTER(TensorView), ctypes.POINTER(TensorView),
+                                  ctypes.POINTER(TensorView), Conv2dParams]
+    lib.tracea_conv2d.restype = ctypes.c_int
+    lib.tracea_conv2d_v0.argtypes = [TensorView, TensorView, ctypes.POINTER(TensorView),
+                                     ctypes.POINTER(TensorView), Conv2dParamsV0]
+    lib.tracea_conv2d_v0.restype = ctypes.c_int
+    lib.tracea_get_last_error.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+    lib.tracea_get_last_error.restype = ctypes.c_int32
+    lib.tracea_clear_error.argtypes = []
+    lib.tracea_clear_error.restype = None
+    for name in ("tracea_version_major", "tracea_version_minor", "tracea_version_patch"):
+        getattr(lib, name).argtypes = []
+        getattr(lib, name).restype = ctypes.c_uint32
+    lib.tracea_init.argtypes = []
+    lib.tracea_init.restype = ctypes.c_int
+    lib.tracea_shutdown.argtypes = []
+    lib.tracea_shutdown.restype = None
+    lib.tracea_b200_device_status.argtypes = [ctypes.c_int32]
+    lib.tracea_b200_device_status.restype = ctypes.c_uint32
+    _lib = lib
+    return lib
+
+
+def last_error():
+    buf = ctypes.create_string_buffer(1024)
+    n = load().tracea_get_last_error(buf, len(buf))
+    return buf.raw[:n].decode("utf-8", "replace") if n > 0 else ""
+
+
+class View:
+    """Owns the shape/stride arrays a TensorView borrows (the caller-owned arrays of
+    include/tracea.hpp:56-66)."""
+
+    def __init__(self, ptr, shape, stride, dtype, device_id):
+        self._shape = (ctypes.c_uint64 * len(shape))(*[int(s) for s in shape])
+        self._stride = (ctypes.c_int64 * len(shape))(*[int(s) for s in stride]) if stride is not None else None
+        self.c = TensorView(ctypes.c_void_p(ptr), len(shape), self._shape,
+                            self._stride if self._stride is not None else ctypes.POINTER(ctypes.c_int64)(),
+                            int(dtype), int(device_id))
+
+
+def conv2d_raw(x, w, bias, residual, out, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1,
+               epilogue=EPILOGUE_IDENTITY, stream=0, check=True):
+    """Call tracea_conv2d with View objects. Returns the status; raises TraceaError when ``check``."""
+    lib = load()
+    p = Conv2dParams(stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1], groups,
+                     int(epilogue), ctypes.c_void_p(stream))
+    st = lib.tracea_conv2d(x.c, w.c, ctypes.byref(bias.c) if bias is not None else None,
+                           ctypes.byref(residual.c) if residual is not None else None,
+                           ctypes.byref(out.c) if out is not None else None, p)
+    if check and st != SUCCESS:
+        raise TraceaError(st, last_error())
+    return st
