@@ -66,6 +66,7 @@ struct ConvKernelArgs {
   long long res_sn, res_sh, res_sw, res_sc;
   int res_vec;
   int act;
+  int out_tma;            // 1: out is dense row-major [M][pitch] and is written by TMA stores
   // error reporting: 4 words {code, block, detail, 0}; first error wins
   uint32_t* status;
 };
@@ -87,13 +88,31 @@ template <> struct OutTraits<float> {
   __device__ static float from_f(float v) { return v; }
 };
 
-// Activation formulas follow src/kernels/gpu/epilogue.cuh:12-63 (fp32 math).
-__device__ __forceinline__ float apply_act(float x, int act) {
-  switch (act) {
-    case kActRelu: return fmaxf(0.0f, x);
-    case kActGelu: return 0.5f * x * (1.0f + tanhf(0.79788456f * (x + 0.044715f * x * x * x)));
-    case kActSilu: return x / (1.0f + expf(-x));
-    default: return x;
+// Activation formulas follow src/kernels/gpu/epilogue.cuh:12-63 (fp32 math). The branch on the
+// activation kind is taken once per 32-value block, not per value. For 16-bit outputs exp / tanh
+// use the hardware approximations (error far below the output rounding); fp32 outputs keep the
+// library functions.
+template <bool kFast>
+__device__ __forceinline__ void apply_act32(float (&f)[32], int act) {
+  if (act == kActRelu) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = fmaxf(0.0f, f[j]);
+  } else if (act == kActSilu) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if constexpr (kFast) f[j] = __fdividef(f[j], 1.0f + __expf(-f[j]));
+      else f[j] = f[j] / (1.0f + expf(-f[j]));
+    }
+  } else if (act == kActGelu) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float x = f[j];
+      const float u = 0.79788456f * (x + 0.044715f * x * x * x);
+      float t;
+      if constexpr (kFast) asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+      else t = tanhf(u);
+      f[j] = 0.5f * x * (1.0f + t);
+    }
   }
 }
 
@@ -107,15 +126,44 @@ __device__ __forceinline__ void report_error(const ConvKernelArgs& a, volatile u
   }
 }
 
-// Dynamic shared memory size the kernel needs for (BN, stages): stages + 1 KB alignment slack + barriers.
+// Shared memory map (offsets from a 1024-byte aligned base):
+//   [0, stages * stage_bytes)        operand ring: per stage A (128 rows x 128 B) then B (BN rows x 128 B)
+//   + kStagingBytes                  4 x 4 KB output staging, one 32-row x 128 B box per epilogue warp
+//   + 4 * BN * 4                     per-epilogue-warp copy of the tile's bias, as fp32
+//   + 256                            mbarriers, TMEM base slot, abort flag
+constexpr int kStagingBytes = 4 * 32 * 128;
 __host__ __device__ constexpr int conv_smem_bytes(int bn, int stages) {
-  return stages * (kBlockM * kStageKBytes + bn * kStageKBytes) + 1024 + 512;
+  return stages * (kBlockM * kStageKBytes + bn * kStageKBytes) + kStagingBytes + 4 * bn * 4 + 256 + 1024;
+}
+
+// 8 consecutive fp32 values -> one 16-byte vector of OutT (16-bit types) / 4 values (fp32).
+template <typename OutT>
+__device__ __forceinline__ uint4 pack16(const float* f) {
+  uint4 r;
+  if constexpr (sizeof(OutT) == 4) {
+    r.x = __float_as_uint(f[0]); r.y = __float_as_uint(f[1]);
+    r.z = __float_as_uint(f[2]); r.w = __float_as_uint(f[3]);
+  } else {
+    OutT* e = reinterpret_cast<OutT*>(&r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = OutTraits<OutT>::from_f(f[j]);
+  }
+  return r;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void add16(float* f, const uint4& raw) {
+  constexpr int kVec = 16 / sizeof(OutT);
+  const OutT* e = reinterpret_cast<const OutT*>(&raw);
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) f[j] += OutTraits<OutT>::to_f(e[j]);
 }
 
 template <typename OutT, int BN>
 __global__ void __launch_bounds__(kNumThreads, 1)
 conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ CUtensorMap tmap_w,
+                          const __grid_constant__ CUtensorMap tmap_out,
                           const __grid_constant__ ConvKernelArgs args) {
   using namespace ptx;
   constexpr uint32_t kABytes = kBlockM * kStageKBytes;   // 16 KB
@@ -126,21 +174,21 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const int num_stages = args.num_stages;
-  // barriers live after the stage buffers
-  const uint32_t bar_base = smem_base + static_cast<uint32_t>(num_stages) * kStageBytes;
+  const uint32_t ring_bytes = static_cast<uint32_t>(num_stages) * kStageBytes;
+  const uint32_t staging_base = smem_base + ring_bytes;
+  const uint32_t bias_off = ring_bytes + kStagingBytes;
+  const uint32_t bar_off = bias_off + 4u * BN * 4u;
+  const uint32_t bar_base = smem_base + bar_off;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 2 + b); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxStages + 4);
-  const uint32_t abort_slot = tmem_slot + 4u;
-  // generic pointers to the two words above
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(
-      smem_gen + static_cast<size_t>(num_stages) * kStageBytes + 8u * (2 * kMaxStages + 4));
+  volatile uint32_t* tmem_slot_p =
+      reinterpret_cast<volatile uint32_t*>(smem_gen + bar_off + 8u * (2 * kMaxStages + 4));
   volatile uint32_t* abort_p = tmem_slot_p + 1;
-  (void)abort_slot;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -158,6 +206,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     fence_mbar_init();
     prefetch_tmap(&tmap_x);
     prefetch_tmap(&tmap_w);
+    if (args.out_tma) prefetch_tmap(&tmap_out);
   }
   if (warp == 1) {
     tmem_alloc<kTmemCols>(tmem_slot);
@@ -287,11 +336,20 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
   } else {
     // ------------------------------------------------------------ epilogue warps (2..5)
-    const int quarter = warp & 3;                 // TMEM lanes [32*quarter, 32*quarter+32)
+    // Warp w may only read TMEM lanes [32*(w%4), 32*(w%4)+32): it owns those 32 output pixels of
+    // the tile, one pixel per lane.
+    const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     OutT* __restrict__ out = static_cast<OutT*>(args.out);
     const OutT* __restrict__ res = static_cast<const OutT*>(args.residual);
-    constexpr int kVec = 16 / sizeof(OutT);       // elements per 16-byte vector
+    constexpr int kVec = 16 / sizeof(OutT);        // elements per 16-byte vector
+    constexpr int kGroupCols = 128 / sizeof(OutT); // columns per 128-byte staging row
+    constexpr int kGroups = BN / kGroupCols;
+    constexpr int kLdPerGroup = kGroupCols / 32;
+    float* bias_w = reinterpret_cast<float*>(smem_gen + bias_off) + quarter * BN;
+    const uint32_t stg = staging_base + static_cast<uint32_t>(quarter) * 4096u;
+    const bool use_res_vec = (res != nullptr) && args.res_vec;
+    int bias_tile = -1;
     int local_tile = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -299,13 +357,24 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int n_tile = tile - m_tile * args.num_n_tiles;
       const int buf = local_tile & 1;
       const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
-      const bool ready = mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_p, kWaitLimitCycles);
-      if (!__all_sync(0xffffffffu, ready)) {      // keep the warp converged for tcgen05.ld
-        if (lane == 0) report_error(args, abort_p, kErrEpilogueWait, (uint32_t)local_tile);
-        ok = false;
-        break;
+      const int n_base = n_tile * BN;
+
+      // this warp's fp32 copy of the tile's bias (zeros when there is none / past K_out)
+      if (n_tile != bias_tile) {
+        __syncwarp();
+        for (int i = lane; i < BN; i += 32) {
+          const int n = n_base + i;
+          float b = 0.0f;
+          if (args.bias != nullptr && n < args.K_out) {
+            b = args.bias_is_f32 ? __ldg(static_cast<const float*>(args.bias) + n)
+                                 : OutTraits<OutT>::to_f(static_cast<const OutT*>(args.bias)[n]);
+          }
+          bias_w[i] = b;
+        }
+        __syncwarp();
+        bias_tile = n_tile;
       }
-      tc_fence_after();
+
       const int m = m_tile * kBlockM + row;
       const bool row_ok = m < args.M;
       const int pq = m / args.Wo;
@@ -314,79 +383,101 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int ho = pq - img * args.Ho;
       const long long out_off = img * args.out_sn + ho * args.out_sh + wo * args.out_sw;
       const long long res_off = img * args.res_sn + ho * args.res_sh + wo * args.res_sw;
+      const OutT* res_row = res + res_off + static_cast<long long>(n_base) * args.res_sc;
+
+      // residual for column group g, 8 x 16 B of this lane's pixel; issued one group ahead of its use
+      uint4 rv[2][8];
+      auto load_res_group = [&](uint4 (&dst)[8], int g) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int n = n_base + g * kGroupCols + c * kVec;
+          if (row_ok && n < args.K_out)
+            dst[c] = __ldg(reinterpret_cast<const uint4*>(res_row + g * kGroupCols) + c);
+          else
+            dst[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      if (use_res_vec) load_res_group(rv[0], 0);
+
+      const bool ready = mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_p, kWaitLimitCycles);
+      if (!__all_sync(0xffffffffu, ready)) {      // keep the warp converged for tcgen05.ld
+        if (lane == 0) report_error(args, abort_p, kErrEpilogueWait, (uint32_t)local_tile);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
       const uint32_t taddr0 =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr0 + c * 32, v);
-        tmem_ld_wait();
-        const int n0 = n_tile * BN + c * 32;
-        if (n0 >= args.K_out) continue;           // warp-uniform
-        float f[32];
+
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-        const bool full_n = (n0 + 32 <= args.K_out);
-        if (args.bias != nullptr) {
-          if (args.bias_is_f32) {
-            const float* bp = static_cast<const float*>(args.bias) + n0;
+      for (int g = 0; g < kGroups; ++g) {
+        if (use_res_vec && g + 1 < kGroups) load_res_group(rv[(g + 1) & 1], g + 1);
+        const int n0 = n_base + g * kGroupCols;
+        const bool group_live = n0 < args.K_out;   // warp-uniform: false when the group is past K_out
+        uint4 packed[8];
+        constexpr int kChunksPerLd = 32 / kVec;    // 16-byte chunks produced per 32-column TMEM load
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full_n || n0 + j < args.K_out) f[j] += __ldg(bp + j);
-          } else {
-            const OutT* bp = static_cast<const OutT*>(args.bias) + n0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full_n || n0 + j < args.K_out) f[j] += OutTraits<OutT>::to_f(bp[j]);
+        for (int h = 0; h < kLdPerGroup; ++h) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr0 + g * kGroupCols + h * 32, v);
+          tmem_ld_wait();
+          if (g == kGroups - 1 && h == kLdPerGroup - 1) {
+            // the accumulator is in registers now: hand the TMEM buffer back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
           }
-        }
-        if (row_ok) {
+          if (!group_live) continue;
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) + bias_w[g * kGroupCols + h * 32 + j];
           if (res != nullptr) {
-            const OutT* rp = res + res_off + n0 * args.res_sc;
-            if (args.res_vec) {
+            if (use_res_vec) {
 #pragma unroll
-              for (int g = 0; g < 32 / kVec; ++g) {
-                if (full_n || n0 + g * kVec < args.K_out) {
-                  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(rp) + g);
-                  const OutT* e = reinterpret_cast<const OutT*>(&raw);
-#pragma unroll
-                  for (int j = 0; j < kVec; ++j) f[g * kVec + j] += OutTraits<OutT>::to_f(e[j]);
-                }
-              }
-            } else {
+              for (int c = 0; c < kChunksPerLd; ++c) add16<OutT>(f + c * kVec, rv[g & 1][h * kChunksPerLd + c]);
+            } else if (row_ok) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (full_n || n0 + j < args.K_out) f[j] += OutTraits<OutT>::to_f(rp[j * args.res_sc]);
+                if (n0 + h * 32 + j < args.K_out)
+                  f[j] += OutTraits<OutT>::to_f(res_row[(g * kGroupCols + h * 32 + j) * args.res_sc]);
             }
           }
-          if (args.act != kActNone) {
+          apply_act32<sizeof(OutT) == 2>(f, args.act);
+          if (args.out_tma || args.out_vec) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = apply_act(f[j], args.act);
-          }
-          OutT* op = out + out_off + n0 * args.out_sc;
-          if (args.out_vec) {
-#pragma unroll
-            for (int g = 0; g < 32 / kVec; ++g) {
-              if (full_n || n0 + g * kVec < args.K_out) {
-                uint4 raw;
-                OutT* e = reinterpret_cast<OutT*>(&raw);
-#pragma unroll
-                for (int j = 0; j < kVec; ++j) e[j] = OutTraits<OutT>::from_f(f[g * kVec + j]);
-                reinterpret_cast<uint4*>(op)[g] = raw;
-              }
-            }
-          } else {
+            for (int c = 0; c < kChunksPerLd; ++c) packed[h * kChunksPerLd + c] = pack16<OutT>(f + c * kVec);
+          } else if (row_ok) {
+            // lanes are consecutive pixels: for NCHW memory (sw == 1) each store instruction is coalesced
+            OutT* op = out + out_off + static_cast<long long>(n0 + h * 32) * args.out_sc;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (full_n || n0 + j < args.K_out) op[j * args.out_sc] = OutTraits<OutT>::from_f(f[j]);
+              if (n0 + h * 32 + j < args.K_out) op[j * args.out_sc] = OutTraits<OutT>::from_f(f[j]);
           }
         }
+        if (!group_live) continue;
+        if (args.out_tma) {
+          // lane's pixel row -> its 128-byte row of the warp's staging box, 16-byte chunks XOR-swizzled
+          // the way the tensor map (SWIZZLE_128B) expects; one TMA store writes the 32 x 128 B box.
+          if (lane == 0) bulk_wait_group_read0();  // previous box has been read out of staging
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            st_shared_v4(stg + lane * 128u + ((static_cast<uint32_t>(c) ^ (lane & 7u)) << 4), packed[c]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_out, stg, n0, m_tile * kBlockM + quarter * 32);
+            bulk_commit_group();
+          }
+        } else if (args.out_vec && row_ok) {
+          OutT* op = out + out_off + static_cast<long long>(n0) * args.out_sc;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            if (n0 + c * kVec < args.K_out) reinterpret_cast<uint4*>(op)[c] = packed[c];
+        }
       }
-      // accumulator drained: hand the TMEM buffer back to the MMA issuer
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(buf));
     }
+    if (args.out_tma && lane == 0) bulk_wait_group0();
   }
 
   // ---------------------------------------------------------------- teardown

@@ -289,29 +289,30 @@ int pick_bn(long long m_tiles, int k_out, int num_sms) {
 
 int pick_stages(int bn) {
   const int stage_bytes = tb200::kBlockM * tb200::kStageKBytes + bn * tb200::kStageKBytes;
-  int s = (232448 - 1536) / stage_bytes;  // 227 KB opt-in limit per CTA
+  const int fixed = tb200::conv_smem_bytes(bn, 0);
+  int s = (232448 - fixed) / stage_bytes;  // 227 KB opt-in limit per CTA
   return std::min(s, tb200::kMaxStages);
 }
 
 template <typename OutT, int BN>
 void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, const CUtensorMap& tw,
-                const ConvKernelArgs& args, int grid, int smem, cudaStream_t stream) {
+                const CUtensorMap& to, const ConvKernelArgs& args, int grid, int smem, cudaStream_t stream) {
   auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN>;
   if (!st.attr_set[dt_idx][bn_idx]) {
     TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     st.attr_set[dt_idx][bn_idx] = true;
   }
-  kern<<<grid, tb200::kNumThreads, smem, stream>>>(tx, tw, args);
+  kern<<<grid, tb200::kNumThreads, smem, stream>>>(tx, tw, to, args);
   TB_CUDA(cudaGetLastError());
 }
 
 template <typename OutT>
 void launch_bn(DeviceState& st, int dt_idx, int bn, const CUtensorMap& tx, const CUtensorMap& tw,
-               const ConvKernelArgs& args, int grid, int smem, cudaStream_t stream) {
+               const CUtensorMap& to, const ConvKernelArgs& args, int grid, int smem, cudaStream_t stream) {
   switch (bn) {
-    case 64: launch_one<OutT, 64>(st, dt_idx, 0, tx, tw, args, grid, smem, stream); break;
-    case 128: launch_one<OutT, 128>(st, dt_idx, 1, tx, tw, args, grid, smem, stream); break;
-    default: launch_one<OutT, 256>(st, dt_idx, 2, tx, tw, args, grid, smem, stream); break;
+    case 64: launch_one<OutT, 64>(st, dt_idx, 0, tx, tw, to, args, grid, smem, stream); break;
+    case 128: launch_one<OutT, 128>(st, dt_idx, 1, tx, tw, to, args, grid, smem, stream); break;
+    default: launch_one<OutT, 256>(st, dt_idx, 2, tx, tw, to, args, grid, smem, stream); break;
   }
 }
 
@@ -454,7 +455,8 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
   const int smem = tb200::conv_smem_bytes(bn, stages);
 
   // ---- tensor maps
-  CUtensorMap tmap_x, tmap_w;
+  CUtensorMap tmap_x, tmap_w, tmap_out;
+  memset(&tmap_out, 0, sizeof(tmap_out));
   // A 1x1 / stride-1 / unpadded conv over dense NHWC memory is a plain [M][C] x [C][K] GEMM; the
   // tiled map is kept as a cross-check of the im2col path (TRACEA_B200_TILED_A=1).
   const bool a_tiled = env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
@@ -559,6 +561,20 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
            (v.stride[2] * es) % 16 == 0 && (v.stride[3] * es) % 16 == 0 && (K % vec_elems) == 0;
   };
   a.out_vec = vec_legal(out) ? 1 : 0;
+  // Output rows that are linear in m = (n*Ho + ho)*Wo + wo form a [M][pitch] matrix: the epilogue
+  // stages 32-pixel x 128-byte boxes in shared memory and the TMA unit writes them out.
+  const bool out_rows_linear = out.stride[2] == Wo * out.stride[3] && out.stride[0] == Ho * out.stride[2];
+  if (a.out_vec && out_rows_linear && env_int("TRACEA_B200_NO_TMA_STORE", 0) == 0) {
+    const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t gstr[1] = {(cuuint64_t)(out.stride[3] * es)};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = g_encode_tiled(&tmap_out, tmap_dtype(x.dtype), 2, out.ptr, gdim, gstr, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled (out) failed with %d", (int)r);
+    a.out_tma = 1;
+  }
   if (epi.bias && bias != nullptr) {
     a.bias = bias->ptr;
     a.bias_is_f32 = bias->dtype == TRACEA_DTYPE_FLOAT32 ? 1 : 0;
@@ -578,13 +594,13 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
   const int grid = static_cast<int>(std::min<long long>(tiles, st.num_sms));
   switch (x.dtype) {
     case TRACEA_DTYPE_BFLOAT16:
-      launch_bn<__nv_bfloat16>(st, 0, bn, tmap_x, tmap_w, a, grid, smem, stream);
+      launch_bn<__nv_bfloat16>(st, 0, bn, tmap_x, tmap_w, tmap_out, a, grid, smem, stream);
       break;
     case TRACEA_DTYPE_FLOAT16:
-      launch_bn<__half>(st, 1, bn, tmap_x, tmap_w, a, grid, smem, stream);
+      launch_bn<__half>(st, 1, bn, tmap_x, tmap_w, tmap_out, a, grid, smem, stream);
       break;
     default:
-      launch_bn<float>(st, 2, bn, tmap_x, tmap_w, a, grid, smem, stream);
+      launch_bn<float>(st, 2, bn, tmap_x, tmap_w, tmap_out, a, grid, smem, stream);
       break;
   }
 }
