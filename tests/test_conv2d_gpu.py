@@ -1,0 +1,432 @@
+"""Parity of the CUDA path against the CPU oracle, through the C ABI, on a B200.
+
+Tolerances (written here once, used everywhere below):
+  fp16 / bf16 inputs, fp32 accumulation:  max|out - ref| <= 1e-2 * max|ref|
+  fp32 inputs computed as TF32:           max|out - ref| <= 5e-3 * max|ref|
+The oracle is fed the inputs already rounded to the storage type, accumulates in fp32 and is rounded
+to the storage type once at the end, like the kernel's single rounding after the epilogue.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import convcases as cc
+from golden.make_golden import CASES
+from oracle import oracle
+from tracea_b200 import ffi, ops, resnet50, runner
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "conv2d_golden.npz"))
+TORCH_DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def to_dev(a, dtype, channels_last=True):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(TORCH_DT[dtype]).cuda()
+    if channels_last and t.ndim == 4:
+        t = t.contiguous(memory_format=torch.channels_last)
+    return t
+
+
+def split_epi(epi):
+    ops_ = [o for o in (epi or "").split("+") if o]
+    act = next((o for o in ops_ if o in ("relu", "silu", "gelu")), "none")
+    return "bias" in ops_, "residual" in ops_, act
+
+
+def run_gpu(x, w, b, res, stride, padding, dilation, epi, dtype, channels_last=True, out_channels_last=None):
+    use_b, use_r, _ = split_epi(epi)
+    tx, tw = to_dev(x, dtype, channels_last), to_dev(w, dtype, channels_last)
+    tb = torch.from_numpy(b).cuda() if use_b else None
+    tr = to_dev(res, dtype, channels_last if out_channels_last is None else out_channels_last) if use_r else None
+    out = ops.conv2d_nchw(tx, tw, tb, tr, stride, padding, dilation, 1, epi or None,
+                          channels_last_out=out_channels_last)
+    torch.cuda.synchronize()
+    assert ffi.load().tracea_b200_device_status(0) == 0
+    return out.float().cpu().numpy()
+
+
+def run_oracle(x, w, b, res, stride, padding, dilation, epi, dtype, fast=True):
+    use_b, use_r, act = split_epi(epi)
+    xr, wr = cc.round_to(x, dtype), cc.round_to(w, dtype)
+    rr = cc.round_to(res, dtype) if use_r else None
+    if fast:
+        out = oracle.conv2d_gemm(cc.channels_last(xr), wr, b if use_b else None, rr, stride, padding, dilation, act)
+    else:
+        out = oracle.conv2d(xr, wr, b if use_b else None, rr, stride, padding, dilation, act)
+    return cc.round_to(np.ascontiguousarray(out), dtype)
+
+
+def check(x, w, b, res, stride, padding, dilation, epi, dtype, **kw):
+    got = run_gpu(x, w, b, res, stride, padding, dilation, epi, dtype, **kw)
+    want = run_oracle(x, w, b, res, stride, padding, dilation, epi, dtype)
+    assert got.shape == want.shape
+    err = cc.rel_err(got, want)
+    assert err <= cc.tol_for(dtype), "rel err %.3g" % err
+    return got, want
+
+
+# --------------------------------------------------------------------------- golden fixtures
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_golden_fixtures(name, dtype):
+    spec = CASES[name]
+    x, w, b, res, ref = (GOLDEN[name + "/" + k] for k in ("x", "w", "b", "res", "out"))
+    got, _ = check(x, w, b, res, spec[7], spec[8], spec[9], spec[10], dtype)
+    if dtype == "f32":   # also directly against the committed fp32 known answers
+        assert cc.rel_err(got, ref) <= cc.TOL_TF32
+
+
+@pytest.mark.parametrize("name", ["verify_conv2d_rs", "bias_relu_3x3", "stem_7x7_s2_c3", "dilated_asym"])
+def test_golden_fixtures_from_nchw_memory(name):
+    """NCHW-contiguous x / OIHW-contiguous w (the layout include/tracea.hpp documents) and NCHW out."""
+    spec = CASES[name]
+    x, w, b, res, ref = (GOLDEN[name + "/" + k] for k in ("x", "w", "b", "res", "out"))
+    got, _ = check(x, w, b, res, spec[7], spec[8], spec[9], spec[10], "f32", channels_last=False,
+                   out_channels_last=False)
+    assert cc.rel_err(got, ref) <= cc.TOL_TF32
+
+
+# --------------------------------------------------------------------------- the five benchmark configs
+def test_config1_fp32_nchw_full():
+    x = cc.uniform((1, 64, 56, 56), 0, "cfg1/x")
+    w = cc.uniform((64, 64, 3, 3), 0, "cfg1/w")
+    b = cc.normal((64,), 0, "cfg1/b", 0.1)
+    got = run_gpu(x, w, b, None, 1, 1, 1, "bias+relu", "f32", channels_last=False, out_channels_last=False)
+    want = oracle.conv2d(x, w, b, None, 1, 1, 1, "relu")          # the scalar restatement, full size
+    assert cc.rel_err(got, want) <= cc.TOL_TF32
+    dig = np.load(os.path.join(os.path.dirname(__file__), "golden", "conv2d_cfg1_digest.npz"))
+    assert np.abs(got.reshape(-1)[::7] - dig["out_every7"]).max() <= cc.TOL_TF32 * float(dig["out_absmax"][0])
+
+
+def test_config2_fp16_readme_shape_full():
+    x = cc.uniform((1, 64, 224, 224), 0, "cfg2/x")
+    w = cc.kaiming((128, 64, 3, 3), 0, "cfg2/w")
+    got, want = check(x, w, None, None, 1, 0, 1, "", "f16", channels_last=False, out_channels_last=False)
+    assert got.shape == (1, 128, 222, 222)      # M = 49284 is not a multiple of the 128-pixel tile
+
+
+def _block_inputs(n):
+    x = np.abs(cc.normal((n, 1024, 14, 14), 0, "cfg3/x"))
+    ws = [cc.kaiming((256, 1024, 1, 1), 0, "cfg3/w1"), cc.kaiming((256, 256, 3, 3), 0, "cfg3/w2"),
+          cc.kaiming((1024, 256, 1, 1), 0, "cfg3/w3")]
+    bs = [cc.normal((k,), 0, "cfg3/b%d" % i, 0.05) for i, k in enumerate((256, 256, 1024))]
+    return x, ws, bs
+
+
+def _block_oracle(x, ws, bs):
+    """Chained oracle: each layer's output is rounded to bf16 before it feeds the next one."""
+    xr = cc.round_to(x, "bf16")
+    y1 = run_oracle(xr, ws[0], bs[0], None, 1, 0, 1, "bias+relu", "bf16")
+    y2 = run_oracle(y1, ws[1], bs[1], None, 1, 1, 1, "bias+relu", "bf16")
+    y3 = run_oracle(y2, ws[2], bs[2], xr, 1, 0, 1, "bias+residual+relu", "bf16")
+    return y1, y2, y3
+
+
+def _block_gpu(x, ws, bs):
+    n = x.shape[0]
+    specs = resnet50.stage3_bottleneck()
+    weights = {sp.name: (torch.from_numpy(w), torch.from_numpy(b)) for sp, w, b in zip(specs, ws, bs)}
+    stack = runner.ConvStack(specs, n, "bf16", "cuda", inputs={"input": to_dev(x, "bf16")}, weights=weights)
+    stack.forward()
+    torch.cuda.synchronize()
+    assert ffi.load().tracea_b200_device_status(0) == 0
+    return stack
+
+
+def test_config3_bottleneck_block_chain_n8_full_tensors():
+    x, ws, bs = _block_inputs(8)
+    stack = _block_gpu(x, ws, bs)
+    y1, y2, y3 = _block_oracle(x, ws, bs)
+    for name, want in (("block.c1", y1), ("block.c2", y2), ("block.out", y3)):
+        got = stack.tensors[name].float().cpu().numpy()
+        assert cc.rel_err(got, want) <= cc.TOL_16BIT, name
+
+
+def test_config3_bottleneck_block_n256_sampled_and_shard_invariant():
+    """Full batch: 2*10^4 output points per layer against fp64 dot products of that layer's actual
+    (GPU-produced, bf16) input, and bit-exact agreement of images 0..7 with the N=8 run."""
+    x, ws, bs = _block_inputs(256)
+    stack = _block_gpu(x, ws, bs)
+    small = _block_gpu(x[:8], ws, bs)
+    for name in ("block.c1", "block.c2", "block.out"):
+        assert torch.equal(stack.tensors[name][:8], small.tensors[name]), name
+    rng = np.random.default_rng(3)
+    xin = stack.tensors["input"].float().cpu().numpy()
+    y1 = stack.tensors["block.c1"].float().cpu().numpy()
+    y2 = stack.tensors["block.c2"].float().cpu().numpy()
+    y3 = stack.tensors["block.out"].float().cpu().numpy()
+    layers = [(xin, ws[0], bs[0], None, 0, "relu", y1), (y1, ws[1], bs[1], None, 1, "relu", y2),
+              (y2, ws[2], bs[2], xin, 0, "relu", y3)]
+    for src, w, b, res, pad, act, got in layers:
+        idx = np.stack([rng.integers(0, s, 20000) for s in got.shape], axis=1)
+        want = oracle.conv2d_points(src, cc.round_to(w, "bf16"), idx, b, res, 1, pad, 1, act, acc_double=True)
+        vals = got[idx[:, 0], idx[:, 1], idx[:, 2], idx[:, 3]]
+        assert np.abs(vals - want).max() <= cc.TOL_16BIT * np.abs(want).max()
+
+
+def test_config4_strided_downsample_bias_silu():
+    # full N = 256 on the GPU; images 0..3 against the oracle in full, 2*10^4 points over the rest
+    n = 256
+    x = cc.normal((n, 128, 56, 56), 0, "cfg4/x")
+    w = cc.kaiming((256, 128, 3, 3), 0, "cfg4/w")
+    b = cc.normal((256,), 0, "cfg4/b", 0.1)
+    got = run_gpu(x, w, b, None, 2, 1, 1, "bias+silu", "bf16")
+    assert got.shape == (n, 256, 28, 28)
+    want4 = run_oracle(x[:4], w, b, None, 2, 1, 1, "bias+silu", "bf16")
+    assert cc.rel_err(got[:4], want4) <= cc.TOL_16BIT
+    rng = np.random.default_rng(4)
+    idx = np.stack([rng.integers(0, s, 20000) for s in got.shape], axis=1)
+    want = oracle.conv2d_points(cc.round_to(x, "bf16"), cc.round_to(w, "bf16"), idx, b, None, 2, 1, 1, "silu")
+    vals = got[idx[:, 0], idx[:, 1], idx[:, 2], idx[:, 3]]
+    assert np.abs(vals - want).max() <= cc.TOL_16BIT * np.abs(want).max()
+
+
+def _stack_inputs(n):
+    img = np.zeros((n, 8, 224, 224), np.float32)          # RGB zero-padded to 8 channels in memory
+    img[:, :3] = cc.normal((n, 3, 224, 224), 0, "cfg5/image")
+    pooled = np.abs(cc.normal((n, 64, 56, 56), 0, "cfg5/pooled"))
+    return img, pooled
+
+
+def test_config5_resnet50_conv_stack_n2_every_layer():
+    """All 53 convs at N=2: every layer's output against the oracle applied to that layer's actual
+    (GPU-produced) input, so one wrong layer cannot hide behind another."""
+    n = 2
+    img, pooled = _stack_inputs(n)
+    specs = resnet50.resnet50_convs()
+    stack = runner.ConvStack(specs, n, "bf16", "cuda", seed=5,
+                             inputs={"image": to_dev(img, "bf16"), "pooled": to_dev(pooled, "bf16")})
+    stack.forward()
+    torch.cuda.synchronize()
+    assert ffi.load().tracea_b200_device_status(0) == 0
+    for sp in specs:
+        src = stack.tensors[sp.src].float().cpu().numpy()
+        w = stack.weights[sp.name].float().cpu().numpy()
+        b = stack.biases[sp.name].cpu().numpy()
+        res = stack.tensors[sp.res].float().cpu().numpy() if sp.res is not None else None
+        _, _, act = split_epi(sp.epilogue)
+        want = oracle.conv2d_gemm(cc.channels_last(src), w, b, res, sp.stride, sp.pad, 1, act)
+        got = stack.tensors[sp.dst].float().cpu().numpy()
+        assert cc.rel_err(got, cc.round_to(np.ascontiguousarray(want), "bf16")) <= cc.TOL_16BIT, sp.name
+
+
+# --------------------------------------------------------------------------- size-independent properties
+def test_identity_filter_reproduces_the_input_bit_exactly_at_full_size():
+    """A 1x1 filter that is the identity matrix copies x to out exactly (x*1 + 0*... in fp32 is
+    exact), which checks every (pixel, channel) address of a full-size tensor."""
+    n, c = 256, 256
+    x = to_dev(cc.normal((n, c, 14, 14), 0, "prop/x"), "bf16")
+    w = torch.eye(c, dtype=torch.bfloat16, device="cuda").view(c, c, 1, 1).contiguous(memory_format=torch.channels_last)
+    out = ops.conv2d_nchw(x, w)
+    assert torch.equal(out, x)
+
+
+def test_shifted_delta_filter_is_an_exact_shift_with_zero_padding():
+    n, c, h = 64, 64, 28
+    x = to_dev(cc.normal((n, c, h, h), 0, "prop/x2"), "bf16")
+    for (r, s) in ((0, 0), (1, 2), (2, 1)):
+        w = torch.zeros(c, c, 3, 3, device="cuda")
+        w[torch.arange(c), torch.arange(c), r, s] = 1.0
+        w = w.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        out = ops.conv2d_nchw(x, w, padding=1)
+        want = torch.zeros_like(x)
+        dh, dw = r - 1, s - 1
+        hs, ws_ = slice(max(0, -dh), h - max(0, dh)), slice(max(0, -dw), h - max(0, dw))
+        hd, wd = slice(max(0, dh), h + min(0, dh)), slice(max(0, dw), h + min(0, dw))
+        want[:, :, hs, ws_] = x[:, :, hd, wd]
+        assert torch.equal(out, want), (r, s)
+
+
+def test_zero_weights_give_activation_of_bias():
+    x = to_dev(cc.normal((4, 64, 9, 9), 0, "prop/x3"), "bf16")
+    w = torch.zeros(96, 64, 3, 3, dtype=torch.bfloat16, device="cuda").contiguous(memory_format=torch.channels_last)
+    b = torch.from_numpy(cc.normal((96,), 0, "prop/b3")).cuda()
+    out = ops.conv2d_nchw(x, w, b, padding=1, epilogue="bias+relu")
+    want = torch.relu(b).to(torch.bfloat16).view(1, -1, 1, 1).expand_as(out)
+    assert torch.equal(out, want)
+
+
+def test_batch_shards_concatenate_to_the_full_batch_bit_exactly():
+    from tracea_b200 import shard
+    n = 37
+    x = to_dev(cc.normal((n, 64, 14, 14), 0, "prop/x4"), "bf16")
+    w = to_dev(cc.kaiming((128, 64, 3, 3), 0, "prop/w4"), "bf16")
+    b = torch.from_numpy(cc.normal((128,), 0, "prop/b4", 0.1)).cuda()
+    full = ops.conv2d_nchw(x, w, b, padding=1, epilogue="bias+silu")
+    for world in (2, 4, 8):
+        parts = []
+        for r in range(world):
+            a, e = shard.shard_range(n, r, world)
+            parts.append(ops.conv2d_nchw(x[a:e], w, b, padding=1, epilogue="bias+silu"))
+        assert torch.equal(torch.cat(parts), full), world
+
+
+# --------------------------------------------------------------------------- edge cases
+EDGE = [
+    # N, C, H, W, K, R, S, stride, pad, dil, epi
+    (1, 64, 1, 1, 64, 1, 1, 1, 0, 1, ""),                  # single pixel
+    (1, 8, 2, 2, 8, 3, 3, 1, 1, 1, "bias"),                # filter larger than the image, kept by padding
+    (3, 64, 15, 15, 64, 3, 3, 1, 1, 1, "bias+relu"),       # M = 675: ragged last tile
+    (1, 64, 16, 16, 72, 3, 3, 1, 1, 1, "bias+relu"),       # K_out tail inside a tile
+    (1, 64, 16, 16, 66, 3, 3, 1, 1, 1, "bias+relu"),       # K_out not a multiple of 8: scalar stores
+    (2, 3, 17, 19, 5, 3, 3, 1, 1, 1, "bias+relu"),         # C = 3: channel-padding adapter
+    (2, 20, 9, 9, 300, 1, 1, 1, 0, 1, "bias"),             # C = 20 (padded to 24), K_out > 256
+    (2, 96, 10, 10, 64, 3, 3, 1, 1, 1, ""),                # 192-byte pixels: 64-byte k-chunks
+    (2, 16, 10, 10, 64, 3, 3, 1, 1, 1, ""),                # 32-byte k-chunks
+    (2, 8, 10, 10, 64, 5, 5, 1, 2, 1, ""),                 # 16-byte k-chunks, odd chunk count
+    (1, 64, 40, 40, 32, 3, 3, (2, 1), (0, 1), 1, "silu"),  # different stride / padding per axis
+    (1, 32, 23, 23, 32, 3, 3, 3, 4, 2, "gelu"),            # stride 3, large padding, dilation 2
+    (1, 64, 32, 32, 64, 7, 7, 2, 3, 1, "bias+relu"),       # 7x7 / 2
+    (5, 64, 7, 7, 2048, 1, 1, 1, 0, 1, "bias+relu"),       # wide output, tiny image
+]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("case", EDGE, ids=lambda c: "N%dC%dH%dW%dK%dR%dS%d" % c[:7])
+def test_edge_cases(case, dtype):
+    N, C, H, W, K, R, S, stride, pad, dil, epi = case
+    x = cc.uniform((N, C, H, W), 1, "edge/x")
+    w = cc.kaiming((K, C, R, S), 1, "edge/w")
+    b = cc.normal((K,), 1, "edge/b", 0.1)
+    ho, wo = oracle.out_shape(x.shape, w.shape, stride, pad, dil)[2:]
+    res = cc.normal((N, K, ho, wo), 1, "edge/res")
+    check(x, w, b, res, stride, pad, dil, epi, dtype)
+
+
+@pytest.mark.parametrize("kind,use_bias,use_res,act", [
+    (ffi.EPILOGUE_IDENTITY, False, False, "none"),
+    (ffi.EPILOGUE_BIAS_ADD, True, False, "none"),
+    (ffi.EPILOGUE_RELU, False, False, "relu"),       # a bias handed to a non-BIAS kind is ignored,
+    (ffi.EPILOGUE_GELU, False, False, "gelu"),       # as in src/interface/c_bindings.rs:144-197
+    (ffi.EPILOGUE_SILU, False, False, "silu"),
+    (ffi.EPILOGUE_BIAS_RELU, True, False, "relu"),
+    (ffi.EPILOGUE_BIAS_SILU, True, False, "silu"),
+    (ffi.EPILOGUE_RESIDUAL, False, True, "none"),
+    (ffi.EPILOGUE_RESIDUAL_RELU, False, True, "relu"),
+    (ffi.EPILOGUE_BIAS_RESIDUAL_RELU, True, True, "relu"),
+    (ffi.EPILOGUE_BIAS_RESIDUAL, True, True, "none"),
+])
+def test_every_epilogue_kind_with_bias_and_residual_both_passed(kind, use_bias, use_res, act):
+    x = cc.uniform((2, 64, 12, 12), 2, "epi/x")
+    w = cc.kaiming((64, 64, 3, 3), 2, "epi/w")
+    b = cc.normal((64,), 2, "epi/b", 0.5)
+    res = cc.normal((2, 64, 12, 12), 2, "epi/res")
+    out = ops.conv2d_nchw(to_dev(x, "bf16"), to_dev(w, "bf16"), torch.from_numpy(b).cuda(), to_dev(res, "bf16"),
+                          1, 1, 1, 1, kind)
+    want = oracle.conv2d_gemm(cc.channels_last(cc.round_to(x, "bf16")), cc.round_to(w, "bf16"),
+                              b if use_bias else None, cc.round_to(res, "bf16") if use_res else None, 1, 1, 1, act)
+    assert cc.rel_err(out.float().cpu().numpy(), cc.round_to(np.ascontiguousarray(want), "bf16")) <= cc.TOL_16BIT
+
+
+def test_bias_silu_kind_without_bias_is_identity():
+    # the reference emits the fused BiasAddSiLU op only when a bias tensor is present
+    x = cc.uniform((1, 64, 8, 8), 2, "epi2/x")
+    w = cc.kaiming((64, 64, 1, 1), 2, "epi2/w")
+    out = ops.conv2d_nchw(to_dev(x, "bf16"), to_dev(w, "bf16"), None, None, 1, 0, 1, 1, ffi.EPILOGUE_BIAS_SILU)
+    want = oracle.conv2d_gemm(cc.channels_last(cc.round_to(x, "bf16")), cc.round_to(w, "bf16"))
+    assert cc.rel_err(out.float().cpu().numpy(), cc.round_to(np.ascontiguousarray(want), "bf16")) <= cc.TOL_16BIT
+
+
+def test_bias_in_the_storage_dtype():
+    x = cc.uniform((1, 64, 8, 8), 2, "bdt/x")
+    w = cc.kaiming((64, 64, 3, 3), 2, "bdt/w")
+    b = cc.normal((64,), 2, "bdt/b", 0.5)
+    out = ops.conv2d_nchw(to_dev(x, "f16"), to_dev(w, "f16"), torch.from_numpy(b).half().cuda(), None, 1, 1, 1, 1,
+                          "bias")
+    want = oracle.conv2d_gemm(cc.channels_last(cc.round_to(x, "f16")), cc.round_to(w, "f16"), cc.round_to(b, "f16"),
+                              None, 1, 1)
+    assert cc.rel_err(out.float().cpu().numpy(), want) <= cc.TOL_16BIT
+
+
+def test_ops_conv2d_nhwc_krsc_surface():
+    """tracea.ops.conv2d: NHWC x, KRSC w, NHWK out (tracea-python/python/tracea/ops.py:39-70)."""
+    x = cc.uniform((2, 64, 10, 12), 3, "ops/x")
+    w = cc.kaiming((32, 64, 3, 3), 3, "ops/w")
+    b = cc.normal((32,), 3, "ops/b", 0.1)
+    x_nhwc = torch.from_numpy(x).permute(0, 2, 3, 1).contiguous().half().cuda()
+    w_krsc = torch.from_numpy(w).permute(0, 2, 3, 1).contiguous().half().cuda()
+    res = cc.normal((2, 10, 12, 32), 3, "ops/res")
+    out = ops.conv2d(x_nhwc, w_krsc, bias=torch.from_numpy(b).cuda(), residual=torch.from_numpy(res).half().cuda(),
+                     epilogue="bias+residual+relu", stride=1, padding=1)
+    assert tuple(out.shape) == (2, 10, 12, 32)
+    want = run_oracle(x, w, b, res.transpose(0, 3, 1, 2), 1, 1, 1, "bias+residual+relu", "f16")
+    assert cc.rel_err(out.float().cpu().numpy().transpose(0, 3, 1, 2), want) <= cc.TOL_16BIT
+
+
+def test_strided_output_view_leaves_the_gaps_alone():
+    """out is a channel slice of a wider NHWC buffer (row pitch 96, K = 64): the other 32 channels
+    must keep their contents."""
+    x = cc.uniform((2, 64, 9, 9), 4, "so/x")
+    w = cc.kaiming((64, 64, 3, 3), 4, "so/w")
+    big = torch.full((2, 96, 9, 9), 7.0, dtype=torch.bfloat16, device="cuda").contiguous(memory_format=torch.channels_last)
+    view = big[:, 16:80]
+    ops.conv2d_into(to_dev(x, "bf16"), to_dev(w, "bf16"), view, None, None, 1, 1)
+    want = run_oracle(x, w, None, None, 1, 1, 1, "", "bf16")
+    assert cc.rel_err(view.float().cpu().numpy(), want) <= cc.TOL_16BIT
+    assert (big[:, :16] == 7.0).all() and (big[:, 80:] == 7.0).all()
+
+
+def test_host_memory_tensors_are_staged_through_the_gpu():
+    """device_id = -1 views: the library copies in, computes on the GPU, copies out and waits."""
+    x = cc.uniform((2, 64, 9, 9), 5, "host/x")
+    w = cc.kaiming((32, 64, 3, 3), 5, "host/w")
+    b = cc.normal((32,), 5, "host/b", 0.1)
+    out = np.full((2, 32, 9, 9), np.nan, np.float32)
+    mk = lambda a: ffi.View(a.ctypes.data, a.shape, [s // 4 for s in a.strides], ffi.DTYPE_FLOAT32, -1)
+    ffi.conv2d_raw(mk(x), mk(w), mk(b), None, mk(out), padding=(1, 1), epilogue=ffi.EPILOGUE_BIAS_RELU)
+    want = oracle.conv2d(x, w, b, None, 1, 1, 1, "relu")
+    assert cc.rel_err(out, want) <= cc.TOL_TF32
+
+
+def test_work_is_enqueued_on_the_callers_stream():
+    x = to_dev(cc.uniform((4, 64, 14, 14), 6, "st/x"), "bf16")
+    w = to_dev(cc.kaiming((64, 64, 3, 3), 6, "st/w"), "bf16")
+    want = ops.conv2d_nchw(x, w, padding=1)
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        got = ops.conv2d_nchw(x, w, padding=1)
+    s.synchronize()
+    assert torch.equal(got, want)
+
+
+def test_five_argument_entry_point_adds_bias_when_given():
+    import ctypes
+    x = cc.uniform((1, 64, 8, 8), 7, "v0/x")
+    w = cc.kaiming((64, 64, 3, 3), 7, "v0/w")
+    b = cc.normal((64,), 7, "v0/b", 0.3)
+    tx, tw, tb = to_dev(x, "bf16"), to_dev(w, "bf16"), torch.from_numpy(b).cuda()
+    out = torch.empty((1, 64, 8, 8), dtype=torch.bfloat16, device="cuda", memory_format=torch.channels_last)
+    vo, vb = ops._view(out), ops._view(tb)
+    p = ffi.Conv2dParamsV0(1, 1, 1, 1, 1, 1, 1, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    st = ffi.load().tracea_conv2d_v0(ops._view(tx).c, ops._view(tw).c, ctypes.byref(vb.c), ctypes.byref(vo.c), p)
+    assert st == ffi.SUCCESS
+    torch.cuda.synchronize()
+    want = run_oracle(x, w, b, None, 1, 1, 1, "bias", "bf16")
+    assert cc.rel_err(out.float().cpu().numpy(), want) <= cc.TOL_16BIT
+
+
+def test_unsupported_on_device_configurations_report_a_status():
+    x = to_dev(cc.uniform((1, 64, 40, 40), 8, "un/x"), "bf16")
+    w = to_dev(cc.kaiming((64, 64, 3, 3), 8, "un/w"), "bf16")
+    with pytest.raises(ffi.TraceaError) as e:
+        ops.conv2d_nchw(x, w, stride=9)            # the TMA traversal stride tops out at 8
+    assert e.value.status == ffi.UNSUPPORTED_CONFIG
+    with pytest.raises(ffi.TraceaError) as e:
+        ops.conv2d_nchw(x, w, groups=2)
+    assert e.value.status == ffi.UNSUPPORTED_CONFIG
+
+
+def test_large_m_many_waves():
+    """M = 2^20 output pixels (8192 tiles, many persistent-loop iterations per CTA)."""
+    x = cc.uniform((16, 64, 256, 256), 9, "big/x")
+    w = cc.kaiming((64, 64, 1, 1), 9, "big/w")
+    got = run_gpu(x, w, None, None, 1, 0, 1, "", "bf16")
+    rng = np.random.default_rng(9)
+    idx = np.stack([rng.integers(0, s, 20000) for s in got.shape], axis=1)
+    want = oracle.conv2d_points(cc.round_to(x, "bf16"), cc.round_to(w, "bf16"), idx)
+    vals = got[idx[:, 0], idx[:, 1], idx[:, 2], idx[:, 3]]
+    assert np.abs(vals - want).max() <= cc.TOL_16BIT * np.abs(want).max()

@@ -194,7 +194,8 @@ View4 load_view4(const TraceaTensorView& v, const char* name) {
   o.device = v.device_id;
   for (int i = 0; i < 4; ++i) {
     o.shape[i] = static_cast<long long>(v.shape[i]);
-    if (o.shape[i] <= 0 || o.shape[i] > 0x7fffffffLL)
+    // an empty batch (shape[0] == 0) is legal and is a no-op; every other extent must be positive
+    if ((o.shape[i] <= 0 && !(i == 0 && o.shape[i] == 0)) || o.shape[i] > 0x7fffffffLL)
       TB_FAIL(TRACEA_INVALID_PARAMS, "%s: shape[%d] = %llu is out of range", name, i,
               (unsigned long long)v.shape[i]);
   }
@@ -658,6 +659,7 @@ void conv2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, cons
   const int dev = x.device;
   if (w.device != dev || out.device != dev)
     TB_FAIL(TRACEA_INVALID_PARAMS, "x, w and out must live on the same device");
+  if (w.shape[0] == 0) TB_FAIL(TRACEA_INVALID_PARAMS, "w: shape[0] = 0 is out of range");
 
   View4 bias4, res4;
   const View4* bias = nullptr;
@@ -692,6 +694,7 @@ void conv2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, cons
     res = &res4;
   }
   const Epilogue epi = decode_epilogue(p.epilogue, bias != nullptr, res != nullptr);
+  if (N == 0) return;  // empty batch: nothing to compute, nothing to launch
 
   if (dev >= 0) {
     conv2d_device(dev, x, w, bias, res, out, p, epi);
