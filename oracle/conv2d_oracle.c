@@ -191,7 +191,9 @@ int oracle_conv2d_gemm(const OracleConvDesc* d, const float* x, const float* w, 
   const long long M = d->N * Ho * Wo, Kg = d->R * d->S * d->C, Nn = d->K;
   const long long Np = (Nn + NR - 1) / NR * NR;
   const long long MC = 96, KC = 384;
-  if (d->xs[1] != 1 || d->xs[3] != d->C || d->xs[2] != d->W * d->C || d->xs[0] != d->H * d->W * d->C)
+  /* dense NHWC memory; the stride of an extent-1 axis carries no information and is not checked */
+  if ((d->C > 1 && d->xs[1] != 1) || (d->W > 1 && d->xs[3] != d->C) || (d->H > 1 && d->xs[2] != d->W * d->C) ||
+      (d->N > 1 && d->xs[0] != d->H * d->W * d->C))
     return -1;
 #ifdef _OPENMP
   if (num_threads > 0) omp_set_num_threads(num_threads);
