@@ -114,6 +114,35 @@ TraceaStatus tracea_conv2d(TraceaTensorView x, TraceaTensorView w, const TraceaT
 TraceaStatus tracea_conv2d_v0(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView *b,
                               TraceaTensorView *out, TraceaConv2dParamsV0 params);
 
+/* tracea_conv2d for callers that must not touch the CUDA allocator. No counterpart in the reference.
+ *
+ * tracea_conv2d borrows staging memory from a stream-ordered pool whenever x arrives NCHW-contiguous
+ * or w OIHW-contiguous (they are rearranged to channels-last before the conv kernel runs). Some
+ * callers cannot afford that: a serving process that handed every free byte of the GPU to its own
+ * arena at start-up (a later allocation fails, or makes the arena give memory back), or a
+ * latency-critical loop where an allocation's implicit synchronisation and driver locks are not
+ * acceptable. This entry point does the same work with the staging area taken from a fixed
+ * 16 MiB array that is part of the library's device image; it never calls cudaMalloc / cudaFree,
+ * the pool allocator, or any library routine that allocates.
+ *
+ * Limits and rules:
+ *   - x, w, b, residual and out must be device tensors (device_id >= 0); host views are rejected
+ *     with INVALID_PARAMS, because staging them would need an allocation.
+ *   - The channels-last copy of x plus the repacked w (each rounded up to 256 bytes) must fit in
+ *     16 MiB; otherwise the call returns UNSUPPORTED_CONFIG and the message states the sizes.
+ *     Channels-last x and w need no staging at all and are accepted at any size.
+ *   - The first call on each device looks up the array's device address (with that device made
+ *     current); issue that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's bytes. The adapters rewrite
+ *     every byte they later read, so nothing depends on old contents, but two calls whose kernels
+ *     can overlap on the GPU (different streams, no ordering between them) race on it. Order such
+ *     calls with events or keep them on one stream.
+ *   - The array is resident on every GPU that loads the library, until the process exits.
+ * Arguments, epilogue rules, validation and status codes are those of tracea_conv2d. */
+TraceaStatus tracea_conv2d_noalloc(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView *b,
+                                   const TraceaTensorView *residual, TraceaTensorView *out,
+                                   TraceaConv2dParams params);
+
 /* Thread-local last error text: tracea-ffi/src/lib.rs:87-109. Returns bytes copied (without the
  * terminating NUL), -1 when buf is NULL or len is 0. */
 int32_t tracea_get_last_error(uint8_t *buf, size_t len);

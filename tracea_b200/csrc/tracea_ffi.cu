@@ -339,15 +339,73 @@ int env_int(const char* name, int dflt) {
   return (v != nullptr && *v != '\0') ? atoi(v) : dflt;
 }
 
+// ------------------------------------------------------------------ static scratch (no-alloc entry)
+// Staging memory for tracea_conv2d_noalloc: a fixed array inside the library's device image, so
+// that entry point never has to ask the CUDA allocator for anything. Every GPU that loads the
+// library carries these bytes until the process exits. The symbol below is only a host-side
+// handle; the device address kernels must be given comes from cudaGetSymbolAddress (noalloc_state).
+constexpr size_t kStaticScratchBytes = 16u << 20;   // 16 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Bump allocator over the static array for the duration of one call.
+struct StaticArena {
+  unsigned char* base = nullptr;
+  size_t capacity = 0;
+  size_t used = 0;
+  void* take(size_t bytes, const char* what) {
+    const size_t start = (used + 255u) & ~static_cast<size_t>(255u);
+    if (start + bytes > capacity)
+      TB_FAIL(TRACEA_UNSUPPORTED_CONFIG,
+              "tracea_conv2d_noalloc: staging %s needs %zu bytes on top of %zu already in use, but the "
+              "built-in scratch holds %zu bytes; use tracea_conv2d or pass channels-last tensors",
+              what, bytes, start, capacity);
+    used = start + bytes;
+    return base + start;
+  }
+};
+
+struct NoAllocState {
+  bool ready = false;
+  int num_sms = 0;
+  unsigned char* scratch = nullptr;   // device address of g_static_scratch on this device
+  bool attr_set[3][3] = {};
+};
+NoAllocState g_noalloc[kMaxDevices];
+
+// First call on a device (with that device current, under g_mutex): queries the SM count, resolves
+// the driver entry points and the device address of the static scratch. Nothing here allocates.
+NoAllocState& noalloc_state(int dev) {
+  if (dev < 0 || dev >= kMaxDevices) TB_FAIL(TRACEA_INVALID_PARAMS, "device_id %d out of range", dev);
+  NoAllocState& na = g_noalloc[dev];
+  if (na.ready) return na;
+  int major = 0, sms = 0;
+  TB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "device %d is not sm_100; this library only carries sm_100a kernels", dev);
+  TB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  load_driver_entry_points();
+  void* addr = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&addr, g_static_scratch);
+  if (e != cudaSuccess || addr == nullptr)
+    TB_FAIL(TRACEA_CUDA_ERROR, "cudaGetSymbolAddress(g_static_scratch) failed on device %d: %s", dev,
+            cudaGetErrorString(e));
+  na.num_sms = sms;
+  na.scratch = static_cast<unsigned char*>(addr);
+  na.ready = true;
+  return na;
+}
+
 // ------------------------------------------------------------------ the device path
 // All pointers are device pointers on `dev`. x: [N,C,H,W], w: [K,C,R,S], out: [N,K,Ho,Wo] (logical).
+void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const View4& w_in, const View4* bias,
+                 const View4* residual, const View4& out, const TraceaConv2dParams& p, const Epilogue& epi);
+
 void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* bias,
                    const View4* residual, const View4& out, const TraceaConv2dParams& p,
                    const Epilogue& epi) {
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceGuard guard(dev);
   DeviceState& st = device_state(dev);
-  cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
 
   if (st.status[0] != 0u) {
     const uint32_t code = st.status[0], blk = st.status[1], det = st.status[2];
@@ -356,6 +414,37 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
             "an earlier conv kernel on device %d gave up a bounded wait (code %u, block %u, detail %u)",
             dev, code, blk, det);
   }
+  conv2d_core(st, nullptr, x_in, w_in, bias, residual, out, p, epi);
+}
+
+// Same device path with every staging buffer carved out of the library's static scratch: no call
+// below this point allocates or frees device or pinned memory.
+void conv2d_device_noalloc(int dev, const View4& x_in, const View4& w_in, const View4* bias,
+                           const View4* residual, const View4& out, const TraceaConv2dParams& p,
+                           const Epilogue& epi) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceGuard guard(dev);
+  NoAllocState& na = noalloc_state(dev);
+  DeviceState st;                       // a view for conv2d_core, not a registered device state
+  st.num_sms = na.num_sms;
+  st.status = g_dev[dev].ready ? g_dev[dev].status : nullptr;   // reuse the status word if one exists
+  memcpy(st.attr_set, na.attr_set, sizeof(st.attr_set));
+  StaticArena arena;
+  arena.base = na.scratch;
+  arena.capacity = kStaticScratchBytes;
+  conv2d_core(st, &arena, x_in, w_in, bias, residual, out, p, epi);
+  memcpy(na.attr_set, st.attr_set, sizeof(st.attr_set));
+}
+
+void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const View4& w_in, const View4* bias,
+                 const View4* residual, const View4& out, const TraceaConv2dParams& p, const Epilogue& epi) {
+  cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
+  // staging comes from the stream-ordered pool, or from the static scratch for the no-alloc entry
+  auto staging = [&](Scratch& s, size_t bytes, const char* what) -> void* {
+    if (arena != nullptr) return arena->take(bytes, what);
+    s.alloc(st, bytes, stream);
+    return s.ptr;
+  };
 
   const int es = elem_size(x_in.dtype);
   const long long N = x_in.shape[0], C = x_in.shape[1], H = x_in.shape[2], W = x_in.shape[3];
@@ -380,7 +469,7 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
                         (x.stride[3] * es) % 16 == 0 && (x.stride[2] * es) % 16 == 0 &&
                         (x.stride[0] * es) % 16 == 0 && x.stride[3] >= C;
   if (!x_direct || env_int("TRACEA_B200_FORCE_STAGING", 0)) {
-    x_scratch.alloc(st, static_cast<size_t>(N * H * W * Cp) * es, stream);
+    void* x_stage = staging(x_scratch, static_cast<size_t>(N * H * W * Cp) * es, "the channels-last copy of x");
     dim3 grid(static_cast<unsigned>((H * W + 31) / 32), static_cast<unsigned>((Cp + 31) / 32),
               static_cast<unsigned>(N));
     if (grid.y > 65535u || grid.z > 65535u)
@@ -388,14 +477,14 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
     dim3 block(32, 8);
     if (es == 2)
       tb200::to_channels_last_kernel<uint16_t><<<grid, block, 0, stream>>>(
-          static_cast<const uint16_t*>(x.ptr), static_cast<uint16_t*>(x_scratch.ptr), (int)C, (int)H,
+          static_cast<const uint16_t*>(x.ptr), static_cast<uint16_t*>(x_stage), (int)C, (int)H,
           (int)W, (int)Cp, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
     else
       tb200::to_channels_last_kernel<uint32_t><<<grid, block, 0, stream>>>(
-          static_cast<const uint32_t*>(x.ptr), static_cast<uint32_t*>(x_scratch.ptr), (int)C, (int)H,
+          static_cast<const uint32_t*>(x.ptr), static_cast<uint32_t*>(x_stage), (int)C, (int)H,
           (int)W, (int)Cp, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
     TB_CUDA(cudaGetLastError());
-    x.ptr = x_scratch.ptr;
+    x.ptr = x_stage;
     x.stride[0] = H * W * Cp;
     x.stride[1] = 1;
     x.stride[2] = W * Cp;
@@ -409,19 +498,19 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
                         w_in.stride[2] == S * C && w_in.stride[0] == R * S * C && aligned16(w_in.ptr);
   if (!w_direct) {
     const long long total = K * R * S * Cp;
-    w_scratch.alloc(st, static_cast<size_t>(total) * es, stream);
+    void* w_stage = staging(w_scratch, static_cast<size_t>(total) * es, "the repacked weights");
     const int threads = 256;
     const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
     if (es == 2)
       tb200::pack_weights_krsc_kernel<uint16_t><<<blocks, threads, 0, stream>>>(
-          static_cast<const uint16_t*>(w_in.ptr), static_cast<uint16_t*>(w_scratch.ptr), total, (int)C,
+          static_cast<const uint16_t*>(w_in.ptr), static_cast<uint16_t*>(w_stage), total, (int)C,
           (int)R, (int)S, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
     else
       tb200::pack_weights_krsc_kernel<uint32_t><<<blocks, threads, 0, stream>>>(
-          static_cast<const uint32_t*>(w_in.ptr), static_cast<uint32_t*>(w_scratch.ptr), total, (int)C,
+          static_cast<const uint32_t*>(w_in.ptr), static_cast<uint32_t*>(w_stage), total, (int)C,
           (int)R, (int)S, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
     TB_CUDA(cudaGetLastError());
-    w_ptr = w_scratch.ptr;
+    w_ptr = w_stage;
   }
 
   // ---- k-chunking: the widest power-of-two row (<= 128 B) that divides one pixel's channels
@@ -622,7 +711,8 @@ void stage_in(DeviceState& st, const View4& host, Staged& s, cudaStream_t stream
 
 // ------------------------------------------------------------------ validation + dispatch
 void conv2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, const TraceaTensorView* bv,
-                    const TraceaTensorView* rv, TraceaTensorView* ov, const TraceaConv2dParams& p) {
+                    const TraceaTensorView* rv, TraceaTensorView* ov, const TraceaConv2dParams& p,
+                    bool no_alloc = false) {
   if (xv.ptr == nullptr || wv.ptr == nullptr || ov == nullptr || ov->ptr == nullptr)
     TB_FAIL(TRACEA_INVALID_PARAMS, "Null pointer in input tensors");
   if (p.groups != 1) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "Unsupported groups: %u", p.groups);
@@ -696,6 +786,13 @@ void conv2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, cons
   const Epilogue epi = decode_epilogue(p.epilogue, bias != nullptr, res != nullptr);
   if (N == 0) return;  // empty batch: nothing to compute, nothing to launch
 
+  if (no_alloc) {
+    if (dev < 0)
+      TB_FAIL(TRACEA_INVALID_PARAMS,
+              "tracea_conv2d_noalloc takes device tensors only: staging host memory would need an allocation");
+    conv2d_device_noalloc(dev, x, w, bias, res, out, p, epi);
+    return;
+  }
   if (dev >= 0) {
     conv2d_device(dev, x, w, bias, res, out, p, epi);
     return;
@@ -767,6 +864,12 @@ TraceaStatus tracea_conv2d_v0(TraceaTensorView x, TraceaTensorView w, const Trac
   p.epilogue = b != nullptr ? TRACEA_EPILOGUE_BIAS_ADD : TRACEA_EPILOGUE_IDENTITY;
   p.stream = params.stream;
   return guarded("tracea_conv2d_v0", [&] { conv2d_checked(x, w, b, nullptr, out, p); });
+}
+
+TraceaStatus tracea_conv2d_noalloc(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView* b,
+                                   const TraceaTensorView* residual, TraceaTensorView* out,
+                                   TraceaConv2dParams params) {
+  return guarded("tracea_conv2d_noalloc", [&] { conv2d_checked(x, w, b, residual, out, params, true); });
 }
 
 int32_t tracea_get_last_error(uint8_t* buf, size_t len) {

@@ -22,7 +22,7 @@ DTYPE_FLOAT32, DTYPE_FLOAT16, DTYPE_BFLOAT16, DTYPE_INT32, DTYPE_INT8 = 0, 1, 2,
  EPILOGUE_BIAS_RESIDUAL) = range(11)
 
 EXPORTED_SYMBOLS = (
-    "tracea_conv2d", "tracea_conv2d_v0", "tracea_get_last_error", "tracea_clear_error",
+    "tracea_conv2d", "tracea_conv2d_v0", "tracea_conv2d_noalloc", "tracea_get_last_error", "tracea_clear_error",
     "tracea_version_major", "tracea_version_minor", "tracea_version_patch", "tracea_init",
     "tracea_shutdown", "tracea_b200_device_status",
 )
@@ -85,6 +85,8 @@ def load():
     lib.tracea_conv2d.argtypes = [TensorView, TensorView, ctypes.POINTER(TensorView), ctypes.POINTER(TensorView),
                                   ctypes.POINTER(TensorView), Conv2dParams]
     lib.tracea_conv2d.restype = ctypes.c_int
+    lib.tracea_conv2d_noalloc.argtypes = lib.tracea_conv2d.argtypes
+    lib.tracea_conv2d_noalloc.restype = ctypes.c_int
     lib.tracea_conv2d_v0.argtypes = [TensorView, TensorView, ctypes.POINTER(TensorView),
                                      ctypes.POINTER(TensorView), Conv2dParamsV0]
     lib.tracea_conv2d_v0.restype = ctypes.c_int
@@ -124,12 +126,13 @@ class View:
 
 
 def conv2d_raw(x, w, bias, residual, out, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1,
-               epilogue=EPILOGUE_IDENTITY, stream=0, check=True):
-    """Call tracea_conv2d with View objects. Returns the status; raises TraceaError when ``check``."""
+               epilogue=EPILOGUE_IDENTITY, stream=0, check=True, entry="tracea_conv2d"):
+    """Call tracea_conv2d (or the entry point named by ``entry``, which must share its signature)
+    with View objects. Returns the status; raises TraceaError when ``check``."""
     lib = load()
     p = Conv2dParams(stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1], groups,
                      int(epilogue), ctypes.c_void_p(stream))
-    st = lib.tracea_conv2d(x.c, w.c, ctypes.byref(bias.c) if bias is not None else None,
+    st = getattr(lib, entry)(x.c, w.c, ctypes.byref(bias.c) if bias is not None else None,
                            ctypes.byref(residual.c) if residual is not None else None,
                            ctypes.byref(out.c) if out is not None else None, p)
     if check and st != SUCCESS:
