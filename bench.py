@@ -209,6 +209,15 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize(dev)
 
+    if args.only_layer is not None:
+        # profiling aid: launch one layer of the block a few times and exit (no JSON line)
+        j = [sp.name.split(".")[-1] for sp in specs].index(args.only_layer)
+        for i in range(warmup + steps):
+            stacks[i % n_sets].launch_one(j)
+        barrier()
+        print("launched %s %d times" % (specs[j].name, warmup + steps), flush=True)
+        return
+
     for i in range(warmup):
         stacks[i % n_sets].forward()
     barrier()
@@ -359,6 +368,8 @@ def main():
     ap.add_argument("--no-resnet", action="store_true", help="skip the ResNet-50 conv-stack extra figure")
     ap.add_argument("--resnet-batch", type=int, default=512, help="global batch of the conv-stack figure")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only-layer", choices=["c1", "c2", "c3"], default=None,
+                    help="profiling aid: only launch this layer of the block, print no JSON")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
