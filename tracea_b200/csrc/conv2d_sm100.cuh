@@ -28,6 +28,7 @@ enum : uint32_t {
   kErrMmaWaitFull = 2,    // MMA issuer: a stage's bytes never landed
   kErrMmaWaitTmem = 3,    // MMA issuer: accumulator never drained
   kErrEpilogueWait = 4,   // epilogue: accumulator never became ready
+  kErrResidualWait = 5,   // epilogue: a residual box never landed
 };
 
 enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3 };
@@ -67,6 +68,7 @@ struct ConvKernelArgs {
   int res_vec;
   int act;
   int out_tma;            // 1: out is dense row-major [M][pitch] and is written by TMA stores
+  int res_tma;            // 1: residual is dense row-major too and is TMA-loaded into the staging boxes
   // error reporting: 4 words {code, block, detail, 0}; first error wins
   uint32_t* status;
 };
@@ -128,12 +130,15 @@ __device__ __forceinline__ void report_error(const ConvKernelArgs& a, volatile u
 
 // Shared memory map (offsets from a 1024-byte aligned base):
 //   [0, stages * stage_bytes)        operand ring: per stage A (128 rows x 128 B) then B (BN rows x 128 B)
-//   + kStagingBytes                  4 x 4 KB output staging, one 32-row x 128 B box per epilogue warp
+//   + kStagingBytes                  per epilogue warp 3 rotating 4 KB boxes (32 pixels x 128 B): the residual
+//                                    is TMA-loaded into a box, combined in place, and the box is TMA-stored
 //   + 4 * BN * 4                     per-epilogue-warp copy of the tile's bias, as fp32
 //   + 256                            mbarriers, TMEM base slot, abort flag
-constexpr int kStagingBytes = 4 * 32 * 128;
+constexpr int kStagingBoxBytes = 32 * 128;
+constexpr int kStagingDepth = 3;
+constexpr int kStagingBytes = 4 * kStagingDepth * kStagingBoxBytes;
 __host__ __device__ constexpr int conv_smem_bytes(int bn, int stages) {
-  return stages * (kBlockM * kStageKBytes + bn * kStageKBytes) + kStagingBytes + 4 * bn * 4 + 256 + 1024;
+  return stages * (kBlockM * kStageKBytes + bn * kStageKBytes) + kStagingBytes + 4 * bn * 4 + 512 + 1024;
 }
 
 // 8 consecutive fp32 values -> one 16-byte vector of OutT (16-bit types) / 4 values (fp32).
@@ -164,6 +169,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ CUtensorMap tmap_w,
                           const __grid_constant__ CUtensorMap tmap_out,
+                          const __grid_constant__ CUtensorMap tmap_res,
                           const __grid_constant__ ConvKernelArgs args) {
   using namespace ptx;
   constexpr uint32_t kABytes = kBlockM * kStageKBytes;   // 16 KB
@@ -185,9 +191,10 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 2 + b); };
-  const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxStages + 4);
-  volatile uint32_t* tmem_slot_p =
-      reinterpret_cast<volatile uint32_t*>(smem_gen + bar_off + 8u * (2 * kMaxStages + 4));
+  auto res_bar = [&](int q, int b) { return bar_base + 8u * (2 * kMaxStages + 4 + q * kStagingDepth + b); };
+  constexpr uint32_t kNumBars = 2 * kMaxStages + 4 + 4 * kStagingDepth;
+  const uint32_t tmem_slot = bar_base + 8u * kNumBars;
+  volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(smem_gen + bar_off + 8u * kNumBars);
   volatile uint32_t* abort_p = tmem_slot_p + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -202,11 +209,14 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), 4);   // one arrival per epilogue warp
     }
+    for (int q = 0; q < 4; ++q)
+      for (int b = 0; b < kStagingDepth; ++b) mbar_init(res_bar(q, b), 1);
     *abort_p = 0u;
     fence_mbar_init();
     prefetch_tmap(&tmap_x);
     prefetch_tmap(&tmap_w);
     if (args.out_tma) prefetch_tmap(&tmap_out);
+    if (args.res_tma) prefetch_tmap(&tmap_res);
   }
   if (warp == 1) {
     tmem_alloc<kTmemCols>(tmem_slot);
@@ -221,18 +231,29 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int chunks_per_stage = kStageKBytes / args.chunk_bytes;
   const int k_iters = (args.total_chunks + chunks_per_stage - 1) / chunks_per_stage;
 
+  // Tiles are walked as (m_tile, n_tile) pairs advanced without divisions: tile += gridDim.x.
+  const int tile_step_m = static_cast<int>(gridDim.x) / args.num_n_tiles;
+  const int tile_step_n = static_cast<int>(gridDim.x) % args.num_n_tiles;
+  const int first_m_tile = static_cast<int>(blockIdx.x) / args.num_n_tiles;
+  const int first_n_tile = static_cast<int>(blockIdx.x) % args.num_n_tiles;
+  const uint32_t full_bar0 = bar_base, empty_bar0 = bar_base + 8u * kMaxStages;
+  const uint32_t ring_end = smem_base + ring_bytes;
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    // One thread; the loop body is kept to a handful of instructions per stage, because at
+    // 256 cycles of tensor work per stage (BN = 128) the issuing thread itself can become the limit.
     if (lane == 0) {
-      int stage = 0;
+      uint32_t stage_addr = smem_base;             // A buffer of the current stage
+      uint32_t full_addr = full_bar0, empty_addr = empty_bar0;
       uint32_t phase = 0;
       const uint32_t a_chunk_bytes = kBlockM * args.chunk_bytes;
       const uint32_t b_chunk_bytes = BN * args.chunk_bytes;
+      const bool one_chunk = (chunks_per_stage == 1) && !args.a_tiled;
       bool ok = true;
       int issued = 0;
+      int m_tile = first_m_tile, n_tile = first_n_tile;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m_tile = tile / args.num_n_tiles;
-        const int n_tile = tile - m_tile * args.num_n_tiles;
         const int m0 = m_tile * kBlockM;
         const int q0 = m0 % args.Wo;
         const int t = m0 / args.Wo;
@@ -240,48 +261,81 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int img0 = t / args.Ho;
         const int w_start = q0 * args.stride_w - args.pad_w;
         const int h_start = p0 * args.stride_h - args.pad_h;
-        int chunk = 0, tap_r = 0, tap_s = 0, cc = 0;
-        for (int it = 0; it < k_iters; ++it) {
-          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_p, kWaitLimitCycles)) {
-            report_error(args, abort_p, kErrProducerWait, (uint32_t)it);
-            ok = false;
-            break;
-          }
-          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
-          const uint32_t a_dst = smem_base + stage * kStageBytes;
-          const uint32_t b_dst = a_dst + kABytes;
-          for (int j = 0; j < chunks_per_stage; ++j, ++chunk) {
-            // chunks past the end of Kgemm read zeros: channel coordinate C / column Kgemm are out of range
-            const bool pad_chunk = chunk >= args.total_chunks;
-            const int c_coord = pad_chunk ? args.C : cc * args.chunk_elems;
-            const int k_coord = pad_chunk ? args.total_chunks * args.chunk_elems
-                                          : chunk * args.chunk_elems;
-            if (args.a_tiled) {
-              tma_load_2d(a_dst + j * a_chunk_bytes, &tmap_x, full_bar(stage), c_coord, m0);
-            } else {
-              tma_load_im2col_4d(a_dst + j * a_chunk_bytes, &tmap_x, full_bar(stage), c_coord,
-                                 w_start, h_start, img0, (uint16_t)(tap_s * args.dil_w),
-                                 (uint16_t)(tap_r * args.dil_h));
+        const int n_coord = n_tile * BN;
+        if (one_chunk) {
+          // common case: one 128-byte chunk per stage = 64 (16-bit) or 32 (fp32) channels of one tap
+          int c_coord = 0, k_coord = 0, tap_s = 0;
+          uint32_t off_w = 0, off_h = 0;
+          for (int it = 0; it < k_iters; ++it) {
+            if (!mbar_try_wait(empty_addr, phase ^ 1u) &&
+                !mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) {
+              report_error(args, abort_p, kErrProducerWait, (uint32_t)it);
+              ok = false;
+              break;
             }
-            tma_load_2d(b_dst + j * b_chunk_bytes, &tmap_w, full_bar(stage), k_coord, n_tile * BN);
-            if (!pad_chunk) {
-              if (++cc == args.chunks_per_tap) {
-                cc = 0;
-                if (++tap_s == args.S) { tap_s = 0; ++tap_r; }
+            mbar_arrive_expect_tx(full_addr, kStageBytes);
+            tma_load_im2col_4d(stage_addr, &tmap_x, full_addr, c_coord, w_start, h_start, img0,
+                               (uint16_t)off_w, (uint16_t)off_h);
+            tma_load_2d(stage_addr + kABytes, &tmap_w, full_addr, k_coord, n_coord);
+            k_coord += args.chunk_elems;
+            c_coord += args.chunk_elems;
+            if (c_coord == args.C) {
+              c_coord = 0;
+              off_w += args.dil_w;
+              if (++tap_s == args.S) { tap_s = 0; off_w = 0; off_h += args.dil_h; }
+            }
+            ++issued;
+            stage_addr += kStageBytes; full_addr += 8u; empty_addr += 8u;
+            if (stage_addr == ring_end) { stage_addr = smem_base; full_addr = full_bar0; empty_addr = empty_bar0; phase ^= 1u; }
+          }
+        } else {
+          int chunk = 0, tap_r = 0, tap_s = 0, cc = 0;
+          for (int it = 0; it < k_iters; ++it) {
+            if (!mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) {
+              report_error(args, abort_p, kErrProducerWait, (uint32_t)it);
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(full_addr, kStageBytes);
+            const uint32_t a_dst = stage_addr;
+            const uint32_t b_dst = a_dst + kABytes;
+            for (int j = 0; j < chunks_per_stage; ++j, ++chunk) {
+              // chunks past the end of Kgemm read zeros: channel coordinate C / column Kgemm are out of range
+              const bool pad_chunk = chunk >= args.total_chunks;
+              const int c_coord = pad_chunk ? args.C : cc * args.chunk_elems;
+              const int k_coord = pad_chunk ? args.total_chunks * args.chunk_elems
+                                            : chunk * args.chunk_elems;
+              if (args.a_tiled) {
+                tma_load_2d(a_dst + j * a_chunk_bytes, &tmap_x, full_addr, c_coord, m0);
+              } else {
+                tma_load_im2col_4d(a_dst + j * a_chunk_bytes, &tmap_x, full_addr, c_coord,
+                                   w_start, h_start, img0, (uint16_t)(tap_s * args.dil_w),
+                                   (uint16_t)(tap_r * args.dil_h));
+              }
+              tma_load_2d(b_dst + j * b_chunk_bytes, &tmap_w, full_addr, k_coord, n_coord);
+              if (!pad_chunk) {
+                if (++cc == args.chunks_per_tap) {
+                  cc = 0;
+                  if (++tap_s == args.S) { tap_s = 0; ++tap_r; }
+                }
               }
             }
+            ++issued;
+            stage_addr += kStageBytes; full_addr += 8u; empty_addr += 8u;
+            if (stage_addr == ring_end) { stage_addr = smem_base; full_addr = full_bar0; empty_addr = empty_bar0; phase ^= 1u; }
           }
-          ++issued;
-          if (++stage == num_stages) { stage = 0; phase ^= 1u; }
         }
+        n_tile += tile_step_n; m_tile += tile_step_m;
+        if (n_tile >= args.num_n_tiles) { n_tile -= args.num_n_tiles; ++m_tile; }
       }
       // Never leave with copies in flight into this CTA's shared memory: wait (bounded) until the
       // MMA side has released every stage that was filled.
       if (ok) {
         const int pending = issued < num_stages ? issued : num_stages;
         for (int i = 0; i < pending; ++i) {
-          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_p, kWaitLimitCycles)) break;
-          if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+          if (!mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) break;
+          stage_addr += kStageBytes; empty_addr += 8u;
+          if (stage_addr == ring_end) { stage_addr = smem_base; empty_addr = empty_bar0; phase ^= 1u; }
         }
       } else {
         // aborted: give outstanding copies a bounded time to land before shared memory is released
@@ -291,8 +345,23 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
+    // One thread. Descriptor low words are precomputed per k-slice; per stage they only move by the
+    // stage pitch, so an MMA costs two adds and one instruction here (the tensor pipe needs a new
+    // 128 x BN x 32-byte MMA every BN/2 cycles).
     if (lane == 0) {
-      int stage = 0;
+      constexpr bool kTf32 = OutTraits<OutT>::kTf32;
+      const uint32_t desc_hi = ((args.a_sbo >> 4) & 0x3FFFu) | (1u << 14) | ((args.swizzle_mode & 7u) << 29);
+      uint32_t a_k[4], b_k[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        a_k[k] = ((smem_base + args.a_mma_off[k]) >> 4) | (((args.a_lbo >> 4) & 0x3FFFu) << 16);
+        b_k[k] = ((smem_base + kABytes + args.b_mma_off[k]) >> 4) | (((args.b_lbo >> 4) & 0x3FFFu) << 16);
+      }
+      constexpr uint32_t kStageUnits = kStageBytes >> 4;
+      const uint32_t ring_units = ring_bytes >> 4;
+      const uint32_t idesc = args.idesc;
+      uint32_t s_off = 0;                          // current stage's offset in 16-byte units
+      uint32_t full_addr = full_bar0, empty_addr = empty_bar0;
       uint32_t phase = 0;
       int local_tile = 0;
       bool ok = true;
@@ -307,29 +376,21 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
         for (int it = 0; it < k_iters; ++it) {
-          if (!mbar_wait_bounded(full_bar(stage), phase, abort_p, kWaitLimitCycles)) {
+          if (!mbar_try_wait(full_addr, phase) &&
+              !mbar_wait_bounded(full_addr, phase, abort_p, kWaitLimitCycles)) {
             report_error(args, abort_p, kErrMmaWaitFull, (uint32_t)it);
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a_base = smem_base + stage * kStageBytes;
-          const uint32_t b_base = a_base + kABytes;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t adesc =
-                make_smem_desc(a_base + args.a_mma_off[k], args.a_lbo, args.a_sbo, args.swizzle_mode);
-            const uint64_t bdesc =
-                make_smem_desc(b_base + args.b_mma_off[k], args.b_lbo, args.b_sbo, args.swizzle_mode);
-            const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
-            if constexpr (OutTraits<OutT>::kTf32) {
-              mma_tf32_ss(d_tmem, adesc, bdesc, args.idesc, acc);
-            } else {
-              mma_f16_ss(d_tmem, adesc, bdesc, args.idesc, acc);
-            }
-          }
-          mma_commit(empty_bar(stage));           // stage reusable once these MMAs retire
-          if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+          if (it == 0) mma_ss_lean<kTf32, false>(d_tmem, a_k[0] + s_off, b_k[0] + s_off, desc_hi, idesc);
+          else mma_ss_lean<kTf32, true>(d_tmem, a_k[0] + s_off, b_k[0] + s_off, desc_hi, idesc);
+          mma_ss_lean<kTf32, true>(d_tmem, a_k[1] + s_off, b_k[1] + s_off, desc_hi, idesc);
+          mma_ss_lean<kTf32, true>(d_tmem, a_k[2] + s_off, b_k[2] + s_off, desc_hi, idesc);
+          mma_ss_lean<kTf32, true>(d_tmem, a_k[3] + s_off, b_k[3] + s_off, desc_hi, idesc);
+          mma_commit(empty_addr);                 // stage reusable once these MMAs retire
+          s_off += kStageUnits; full_addr += 8u; empty_addr += 8u;
+          if (s_off == ring_units) { s_off = 0; full_addr = full_bar0; empty_addr = empty_bar0; phase ^= 1u; }
         }
         if (ok) mma_commit(tfull_bar(buf));       // accumulator complete
       }
@@ -337,7 +398,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else {
     // ------------------------------------------------------------ epilogue warps (2..5)
     // Warp w may only read TMEM lanes [32*(w%4), 32*(w%4)+32): it owns those 32 output pixels of
-    // the tile, one pixel per lane.
+    // the tile, one pixel per lane. Columns are processed in groups of 128 bytes of output.
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     OutT* __restrict__ out = static_cast<OutT*>(args.out);
@@ -346,58 +407,83 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     constexpr int kGroupCols = 128 / sizeof(OutT); // columns per 128-byte staging row
     constexpr int kGroups = BN / kGroupCols;
     constexpr int kLdPerGroup = kGroupCols / 32;
+    constexpr int kChunksPerLd = 32 / kVec;        // 16-byte chunks produced per 32-column TMEM load
     float* bias_w = reinterpret_cast<float*>(smem_gen + bias_off) + quarter * BN;
-    const uint32_t stg = staging_base + static_cast<uint32_t>(quarter) * 4096u;
-    const bool use_res_vec = (res != nullptr) && args.res_vec;
+    const uint32_t bias_w_s = smem_base + bias_off + static_cast<uint32_t>(quarter * BN) * 4u;
+    const uint32_t stg0 = staging_base + static_cast<uint32_t>(quarter) * (kStagingDepth * kStagingBoxBytes);
+    const bool res_tma = args.res_tma != 0;
+    // this lane's 16-byte chunk c of its staging row lives at row*128 + ((c ^ (row & 7)) << 4): the
+    // SWIZZLE_128B pattern of the out / residual tensor maps (bank-conflict free for 8-lane phases)
+    const uint32_t lane_row_off = static_cast<uint32_t>(lane) * 128u;
+    const uint32_t lane_xor = static_cast<uint32_t>(lane) & 7u;
+    uint32_t box = 0;                              // staging box the next live group uses (0..2)
+    uint32_t box_phase = 0;                        // bit b = parity of the next residual load into box b
     int bias_tile = -1;
+    constexpr int kBiasPerLane = BN / 32;
+    float bias_next[kBiasPerLane];
+    auto fetch_bias = [&](int nt) {   // independent loads: all in flight together
+#pragma unroll
+      for (int j = 0; j < kBiasPerLane; ++j) {
+        const int n = nt * BN + j * 32 + lane;
+        float b = 0.0f;
+        if (args.bias != nullptr && n < args.K_out) {
+          b = args.bias_is_f32 ? __ldg(static_cast<const float*>(args.bias) + n)
+                               : OutTraits<OutT>::to_f(static_cast<const OutT*>(args.bias)[n]);
+        }
+        bias_next[j] = b;
+      }
+    };
+    if (static_cast<int>(blockIdx.x) < num_tiles) fetch_bias(static_cast<int>(blockIdx.x) % args.num_n_tiles);
     int local_tile = 0;
     bool ok = true;
+    int m_tile = first_m_tile - tile_step_m, n_tile = first_n_tile - tile_step_n;
+    const bool need_coords = !args.out_tma || (res != nullptr && !res_tma);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-      const int m_tile = tile / args.num_n_tiles;
-      const int n_tile = tile - m_tile * args.num_n_tiles;
+      n_tile += tile_step_n; m_tile += tile_step_m;
+      if (n_tile >= args.num_n_tiles) { n_tile -= args.num_n_tiles; ++m_tile; }
+      else if (n_tile < 0) { n_tile += args.num_n_tiles; --m_tile; }
       const int buf = local_tile & 1;
       const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
       const int n_base = n_tile * BN;
+      const int m_row0 = m_tile * kBlockM + quarter * 32;
 
-      // this warp's fp32 copy of the tile's bias (zeros when there is none / past K_out)
+      // this warp's fp32 copy of the tile's bias (zeros when there is none / past K_out); the values
+      // were fetched into registers during the previous tile, and the next tile's are fetched now
       if (n_tile != bias_tile) {
         __syncwarp();
-        for (int i = lane; i < BN; i += 32) {
-          const int n = n_base + i;
-          float b = 0.0f;
-          if (args.bias != nullptr && n < args.K_out) {
-            b = args.bias_is_f32 ? __ldg(static_cast<const float*>(args.bias) + n)
-                                 : OutTraits<OutT>::to_f(static_cast<const OutT*>(args.bias)[n]);
-          }
-          bias_w[i] = b;
-        }
+#pragma unroll
+        for (int j = 0; j < kBiasPerLane; ++j) bias_w[j * 32 + lane] = bias_next[j];
         __syncwarp();
         bias_tile = n_tile;
+      }
+      if (tile + static_cast<int>(gridDim.x) < num_tiles && tile_step_n != 0) {
+        int nn = n_tile + tile_step_n;
+        if (nn >= args.num_n_tiles) nn -= args.num_n_tiles;
+        fetch_bias(nn);
       }
 
       const int m = m_tile * kBlockM + row;
       const bool row_ok = m < args.M;
-      const int pq = m / args.Wo;
-      const int wo = m - pq * args.Wo;
-      const int img = pq / args.Ho;
-      const int ho = pq - img * args.Ho;
-      const long long out_off = img * args.out_sn + ho * args.out_sh + wo * args.out_sw;
-      const long long res_off = img * args.res_sn + ho * args.res_sh + wo * args.res_sw;
+      long long out_off = 0, res_off = 0;
+      if (need_coords) {   // only the per-lane store / load paths need (n, ho, wo); the TMA paths do not
+        const int pq = m / args.Wo;
+        const int wo = m - pq * args.Wo;
+        const int img = pq / args.Ho;
+        const int ho = pq - img * args.Ho;
+        out_off = img * args.out_sn + ho * args.out_sh + wo * args.out_sw;
+        res_off = img * args.res_sn + ho * args.res_sh + wo * args.res_sw;
+      }
       const OutT* res_row = res + res_off + static_cast<long long>(n_base) * args.res_sc;
 
-      // residual for column group g, 8 x 16 B of this lane's pixel; issued one group ahead of its use
-      uint4 rv[2][8];
-      auto load_res_group = [&](uint4 (&dst)[8], int g) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const int n = n_base + g * kGroupCols + c * kVec;
-          if (row_ok && n < args.K_out)
-            dst[c] = __ldg(reinterpret_cast<const uint4*>(res_row + g * kGroupCols) + c);
-          else
-            dst[c] = make_uint4(0u, 0u, 0u, 0u);
+      // Residual box of the tile's first live group: requested before the accumulator is waited for.
+      // Box `box` was last stored from three groups ago; at most the two newer stores may be pending.
+      if (res_tma && n_base < args.K_out) {
+        if (lane == 0) {
+          bulk_wait_group_read<2>();
+          mbar_arrive_expect_tx(res_bar(quarter, box), kStagingBoxBytes);
+          tma_load_2d(stg0 + box * kStagingBoxBytes, &tmap_res, res_bar(quarter, box), n_base, m_row0);
         }
-      };
-      if (use_res_vec) load_res_group(rv[0], 0);
+      }
 
       const bool ready = mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_p, kWaitLimitCycles);
       if (!__all_sync(0xffffffffu, ready)) {      // keep the warp converged for tcgen05.ld
@@ -411,35 +497,77 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
 #pragma unroll
       for (int g = 0; g < kGroups; ++g) {
-        if (use_res_vec && g + 1 < kGroups) load_res_group(rv[(g + 1) & 1], g + 1);
         const int n0 = n_base + g * kGroupCols;
         const bool group_live = n0 < args.K_out;   // warp-uniform: false when the group is past K_out
+        const uint32_t stg = stg0 + box * kStagingBoxBytes;
+        // residual box of the NEXT group goes into the next staging box, whose last store (three groups
+        // back) must have been read out; the store of the previous group may still be pending
+        if (res_tma && g + 1 < kGroups && n0 + kGroupCols < args.K_out) {
+          if (lane == 0) {
+            const uint32_t nb = (box + 1u) % kStagingDepth;
+            bulk_wait_group_read<1>();
+            mbar_arrive_expect_tx(res_bar(quarter, nb), kStagingBoxBytes);
+            tma_load_2d(stg0 + nb * kStagingBoxBytes, &tmap_res, res_bar(quarter, nb), n0 + kGroupCols, m_row0);
+          }
+        }
+        uint32_t v[kLdPerGroup][32];
+#pragma unroll
+        for (int h = 0; h < kLdPerGroup; ++h) tmem_ld_32x32(taddr0 + g * kGroupCols + h * 32, v[h]);
+        tmem_ld_wait();
+        if (g == kGroups - 1) {
+          // the accumulator is in registers now: hand the TMEM buffer back to the MMA issuer
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(buf));
+        }
+        if (!group_live) continue;
+
+        if (res_tma) {
+          const bool landed = mbar_wait_bounded(res_bar(quarter, box), (box_phase >> box) & 1u, abort_p,
+                                                kWaitLimitCycles);
+          if (!__all_sync(0xffffffffu, landed)) {
+            if (lane == 0) report_error(args, abort_p, kErrResidualWait, (uint32_t)local_tile);
+            ok = false;
+            break;
+          }
+          box_phase ^= (1u << box);
+        } else if (args.out_tma) {
+          if (lane == 0) bulk_wait_group_read<2>();   // this box's previous store has been read out
+          __syncwarp();
+        }
+
         uint4 packed[8];
-        constexpr int kChunksPerLd = 32 / kVec;    // 16-byte chunks produced per 32-column TMEM load
 #pragma unroll
         for (int h = 0; h < kLdPerGroup; ++h) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr0 + g * kGroupCols + h * 32, v);
-          tmem_ld_wait();
-          if (g == kGroups - 1 && h == kLdPerGroup - 1) {
-            // the accumulator is in registers now: hand the TMEM buffer back to the MMA issuer
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(buf));
-          }
-          if (!group_live) continue;
           float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) + bias_w[g * kGroupCols + h * 32 + j];
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 b4 = ld_shared_f4(bias_w_s + static_cast<uint32_t>(g * kGroupCols + h * 32 + j4 * 4) * 4u);
+            f[j4 * 4 + 0] = __uint_as_float(v[h][j4 * 4 + 0]) + b4.x;
+            f[j4 * 4 + 1] = __uint_as_float(v[h][j4 * 4 + 1]) + b4.y;
+            f[j4 * 4 + 2] = __uint_as_float(v[h][j4 * 4 + 2]) + b4.z;
+            f[j4 * 4 + 3] = __uint_as_float(v[h][j4 * 4 + 3]) + b4.w;
+          }
           if (res != nullptr) {
-            if (use_res_vec) {
+            if (res_tma) {
 #pragma unroll
-              for (int c = 0; c < kChunksPerLd; ++c) add16<OutT>(f + c * kVec, rv[g & 1][h * kChunksPerLd + c]);
+              for (int c = 0; c < kChunksPerLd; ++c) {
+                const uint32_t cc = static_cast<uint32_t>(h * kChunksPerLd + c);
+                add16<OutT>(f + c * kVec, ld_shared_v4(stg + lane_row_off + ((cc ^ lane_xor) << 4)));
+              }
             } else if (row_ok) {
+              if (args.res_vec) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (n0 + h * 32 + j < args.K_out)
-                  f[j] += OutTraits<OutT>::to_f(res_row[(g * kGroupCols + h * 32 + j) * args.res_sc]);
+                for (int c = 0; c < kChunksPerLd; ++c)
+                  if (n0 + h * 32 + c * kVec < args.K_out)
+                    add16<OutT>(f + c * kVec,
+                                __ldg(reinterpret_cast<const uint4*>(res_row + g * kGroupCols + h * 32) + c));
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n0 + h * 32 + j < args.K_out)
+                    f[j] += OutTraits<OutT>::to_f(res_row[(g * kGroupCols + h * 32 + j) * args.res_sc]);
+              }
             }
           }
           apply_act32<sizeof(OutT) == 2>(f, args.act);
@@ -454,21 +582,18 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
               if (n0 + h * 32 + j < args.K_out) op[j * args.out_sc] = OutTraits<OutT>::from_f(f[j]);
           }
         }
-        if (!group_live) continue;
         if (args.out_tma) {
-          // lane's pixel row -> its 128-byte row of the warp's staging box, 16-byte chunks XOR-swizzled
-          // the way the tensor map (SWIZZLE_128B) expects; one TMA store writes the 32 x 128 B box.
-          if (lane == 0) bulk_wait_group_read0();  // previous box has been read out of staging
-          __syncwarp();
+          // the lane's pixel row goes to its swizzled 128-byte row of the box; one TMA store writes the box
 #pragma unroll
           for (int c = 0; c < 8; ++c)
-            st_shared_v4(stg + lane * 128u + ((static_cast<uint32_t>(c) ^ (lane & 7u)) << 4), packed[c]);
+            st_shared_v4(stg + lane_row_off + ((static_cast<uint32_t>(c) ^ lane_xor) << 4), packed[c]);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmap_out, stg, n0, m_tile * kBlockM + quarter * 32);
+            tma_store_2d(&tmap_out, stg, n0, m_row0);
             bulk_commit_group();
           }
+          box = (box + 1u) % kStagingDepth;
         } else if (args.out_vec && row_ok) {
           OutT* op = out + out_off + static_cast<long long>(n0) * args.out_sc;
 #pragma unroll

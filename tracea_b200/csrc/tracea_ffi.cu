@@ -297,23 +297,25 @@ int pick_stages(int bn) {
 
 template <typename OutT, int BN>
 void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, const CUtensorMap& tw,
-                const CUtensorMap& to, const ConvKernelArgs& args, int grid, int smem, cudaStream_t stream) {
+                const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid, int smem,
+                cudaStream_t stream) {
   auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN>;
   if (!st.attr_set[dt_idx][bn_idx]) {
     TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     st.attr_set[dt_idx][bn_idx] = true;
   }
-  kern<<<grid, tb200::kNumThreads, smem, stream>>>(tx, tw, to, args);
+  kern<<<grid, tb200::kNumThreads, smem, stream>>>(tx, tw, to, tr, args);
   TB_CUDA(cudaGetLastError());
 }
 
 template <typename OutT>
 void launch_bn(DeviceState& st, int dt_idx, int bn, const CUtensorMap& tx, const CUtensorMap& tw,
-               const CUtensorMap& to, const ConvKernelArgs& args, int grid, int smem, cudaStream_t stream) {
+               const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid, int smem,
+               cudaStream_t stream) {
   switch (bn) {
-    case 64: launch_one<OutT, 64>(st, dt_idx, 0, tx, tw, to, args, grid, smem, stream); break;
-    case 128: launch_one<OutT, 128>(st, dt_idx, 1, tx, tw, to, args, grid, smem, stream); break;
-    default: launch_one<OutT, 256>(st, dt_idx, 2, tx, tw, to, args, grid, smem, stream); break;
+    case 64: launch_one<OutT, 64>(st, dt_idx, 0, tx, tw, to, tr, args, grid, smem, stream); break;
+    case 128: launch_one<OutT, 128>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream); break;
+    default: launch_one<OutT, 256>(st, dt_idx, 2, tx, tw, to, tr, args, grid, smem, stream); break;
   }
 }
 
@@ -545,8 +547,9 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   const int smem = tb200::conv_smem_bytes(bn, stages);
 
   // ---- tensor maps
-  CUtensorMap tmap_x, tmap_w, tmap_out;
+  CUtensorMap tmap_x, tmap_w, tmap_out, tmap_res;
   memset(&tmap_out, 0, sizeof(tmap_out));
+  memset(&tmap_res, 0, sizeof(tmap_res));
   // A 1x1 / stride-1 / unpadded conv over dense NHWC memory is a plain [M][C] x [C][K] GEMM; the
   // tiled map is kept as a cross-check of the im2col path (TRACEA_B200_TILED_A=1).
   const bool a_tiled = env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
@@ -676,6 +679,20 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     a.res_sh = residual->stride[2];
     a.res_sw = residual->stride[3];
     a.res_vec = vec_legal(*residual) ? 1 : 0;
+    // a residual with the same dense row-linear form is TMA-loaded into the epilogue's staging boxes
+    const bool res_rows_linear = residual->stride[2] == Wo * residual->stride[3] &&
+                                 residual->stride[0] == Ho * residual->stride[2];
+    if (a.out_tma && a.res_vec && res_rows_linear && env_int("TRACEA_B200_NO_TMA_RESIDUAL", 0) == 0) {
+      const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+      const cuuint64_t gstr[1] = {(cuuint64_t)(residual->stride[3] * es)};
+      const cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32u};
+      const cuuint32_t estr[2] = {1u, 1u};
+      CUresult r = g_encode_tiled(&tmap_res, tmap_dtype(x.dtype), 2, residual->ptr, gdim, gstr, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled (residual) failed with %d", (int)r);
+      a.res_tma = 1;
+    }
   }
   a.act = epi.act;
   a.status = st.status;
@@ -684,13 +701,13 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   const int grid = static_cast<int>(std::min<long long>(tiles, st.num_sms));
   switch (x.dtype) {
     case TRACEA_DTYPE_BFLOAT16:
-      launch_bn<__nv_bfloat16>(st, 0, bn, tmap_x, tmap_w, tmap_out, a, grid, smem, stream);
+      launch_bn<__nv_bfloat16>(st, 0, bn, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
       break;
     case TRACEA_DTYPE_FLOAT16:
-      launch_bn<__half>(st, 1, bn, tmap_x, tmap_w, tmap_out, a, grid, smem, stream);
+      launch_bn<__half>(st, 1, bn, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
       break;
     default:
-      launch_bn<float>(st, 2, bn, tmap_x, tmap_w, tmap_out, a, grid, smem, stream);
+      launch_bn<float>(st, 2, bn, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
       break;
   }
 }
