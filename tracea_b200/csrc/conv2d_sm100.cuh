@@ -13,6 +13,19 @@
 #include <cuda_fp16.h>
 #include "ptx_sm100.cuh"
 
+// Role-level cycle accounting for kernel bring-up: compiled in only with -DTB200_PROFILE, in which
+// case ConvKernelArgs::prof points at 16 counters per CTA (waits and totals per role).
+#ifdef TB200_PROFILE
+#define TB200_PROF_T(var) const long long var = clock64()
+#define TB200_PROF_ADD(acc, t0) acc += clock64() - (t0)
+#define TB200_PROF_STORE(idx, val) \
+  if (args.prof != nullptr) args.prof[blockIdx.x * 16 + (idx)] = (val)
+#else
+#define TB200_PROF_T(var)
+#define TB200_PROF_ADD(acc, t0)
+#define TB200_PROF_STORE(idx, val)
+#endif
+
 namespace tb200 {
 
 constexpr int kBlockM = 128;          // output pixels per tile = TMEM lanes
@@ -71,6 +84,7 @@ struct ConvKernelArgs {
   int res_tma;            // 1: residual is dense row-major too and is TMA-loaded into the staging boxes
   // error reporting: 4 words {code, block, detail, 0}; first error wins
   uint32_t* status;
+  long long* prof;        // cycle counters, only written by -DTB200_PROFILE builds
 };
 
 template <typename T> struct OutTraits;
@@ -164,6 +178,39 @@ __device__ __forceinline__ void add16(float* f, const uint4& raw) {
   for (int j = 0; j < kVec; ++j) f[j] += OutTraits<OutT>::to_f(e[j]);
 }
 
+// Out-of-line path for outputs / residuals the TMA boxes cannot address (NCHW or irregular
+// strides, K_out not a multiple of the vector width): finishes one 32-column block of one pixel --
+// residual, activation, store. `f` holds accumulator + bias. Kept out of line so that the common
+// path's instruction footprint stays small.
+template <typename OutT>
+__device__ __noinline__ void epilogue_block_generic(const ConvKernelArgs& args, float* f, const OutT* res_px,
+                                                    OutT* out_px, int n_first, bool row_ok) {
+  constexpr int kVec = 16 / sizeof(OutT);
+  if (res_px != nullptr && row_ok) {
+    if (args.res_vec) {
+#pragma unroll
+      for (int c = 0; c < 32 / kVec; ++c)
+        if (n_first + c * kVec < args.K_out) add16<OutT>(f + c * kVec, __ldg(reinterpret_cast<const uint4*>(res_px) + c));
+    } else {
+#pragma unroll 4
+      for (int j = 0; j < 32; ++j)
+        if (n_first + j < args.K_out) f[j] += OutTraits<OutT>::to_f(res_px[j * args.res_sc]);
+    }
+  }
+  apply_act32<sizeof(OutT) == 2>(*reinterpret_cast<float(*)[32]>(f), args.act);
+  if (!row_ok) return;
+  if (args.out_vec) {
+#pragma unroll
+    for (int c = 0; c < 32 / kVec; ++c)
+      if (n_first + c * kVec < args.K_out) reinterpret_cast<uint4*>(out_px)[c] = pack16<OutT>(f + c * kVec);
+  } else {
+    // lanes are consecutive pixels: for NCHW memory (sw == 1) each store instruction is coalesced
+#pragma unroll 4
+    for (int j = 0; j < 32; ++j)
+      if (n_first + j < args.K_out) out_px[j * args.out_sc] = OutTraits<OutT>::from_f(f[j]);
+  }
+}
+
 template <typename OutT, int BN>
 __global__ void __launch_bounds__(kNumThreads, 1)
 conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
@@ -253,6 +300,10 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       bool ok = true;
       int issued = 0;
       int m_tile = first_m_tile, n_tile = first_n_tile;
+      long long prof_wait = 0;
+      (void)prof_wait;
+      TB200_PROF_T(prof_t0);
+      bool slot_free = mbar_test_wait(empty_addr, phase ^ 1u);
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = m_tile * kBlockM;
         const int q0 = m0 % args.Wo;
@@ -267,16 +318,20 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           int c_coord = 0, k_coord = 0, tap_s = 0;
           uint32_t off_w = 0, off_h = 0;
           for (int it = 0; it < k_iters; ++it) {
-            if (!mbar_try_wait(empty_addr, phase ^ 1u) &&
-                !mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) {
+            TB200_PROF_T(tw);
+            if (!slot_free && !mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) {
               report_error(args, abort_p, kErrProducerWait, (uint32_t)it);
               ok = false;
               break;
             }
-            mbar_arrive_expect_tx(full_addr, kStageBytes);
-            tma_load_im2col_4d(stage_addr, &tmap_x, full_addr, c_coord, w_start, h_start, img0,
-                               (uint16_t)off_w, (uint16_t)off_h);
-            tma_load_2d(stage_addr + kABytes, &tmap_w, full_addr, k_coord, n_coord);
+            TB200_PROF_ADD(prof_wait, tw);
+            // probe the next slot now; the answer is read at the top of the next iteration
+            uint32_t nstage = stage_addr + kStageBytes, nfull = full_addr + 8u, nempty = empty_addr + 8u, nphase = phase;
+            if (nstage == ring_end) { nstage = smem_base; nfull = full_bar0; nempty = empty_bar0; nphase ^= 1u; }
+            const bool next_free =
+                tma_stage_probe(stage_addr, stage_addr + kABytes, full_addr, kStageBytes, &tmap_x, c_coord, w_start,
+                                h_start, img0, (uint16_t)off_w, (uint16_t)off_h, &tmap_w, k_coord, n_coord, nempty,
+                                nphase ^ 1u);
             k_coord += args.chunk_elems;
             c_coord += args.chunk_elems;
             if (c_coord == args.C) {
@@ -285,8 +340,8 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
               if (++tap_s == args.S) { tap_s = 0; off_w = 0; off_h += args.dil_h; }
             }
             ++issued;
-            stage_addr += kStageBytes; full_addr += 8u; empty_addr += 8u;
-            if (stage_addr == ring_end) { stage_addr = smem_base; full_addr = full_bar0; empty_addr = empty_bar0; phase ^= 1u; }
+            stage_addr = nstage; full_addr = nfull; empty_addr = nempty; phase = nphase;
+            slot_free = next_free;
           }
         } else {
           int chunk = 0, tap_r = 0, tap_s = 0, cc = 0;
@@ -324,10 +379,13 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             stage_addr += kStageBytes; full_addr += 8u; empty_addr += 8u;
             if (stage_addr == ring_end) { stage_addr = smem_base; full_addr = full_bar0; empty_addr = empty_bar0; phase ^= 1u; }
           }
+          slot_free = false;   // this path waits in full every time
         }
         n_tile += tile_step_n; m_tile += tile_step_m;
         if (n_tile >= args.num_n_tiles) { n_tile -= args.num_n_tiles; ++m_tile; }
       }
+      TB200_PROF_STORE(0, prof_wait);
+      TB200_PROF_STORE(1, clock64() - prof_t0);
       // Never leave with copies in flight into this CTA's shared memory: wait (bounded) until the
       // MMA side has released every stage that was filled.
       if (ok) {
@@ -365,35 +423,51 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       uint32_t phase = 0;
       int local_tile = 0;
       bool ok = true;
+      long long prof_wfull = 0, prof_wtmem = 0;
+      (void)prof_wfull; (void)prof_wtmem;
+      TB200_PROF_T(prof_t0);
+      bool stage_ready = mbar_test_wait(full_addr, phase);
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
         const int buf = local_tile & 1;
         const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
+        TB200_PROF_T(tw0);
         if (!mbar_wait_bounded(tempty_bar(buf), (use & 1u) ^ 1u, abort_p, kWaitLimitCycles)) {
           report_error(args, abort_p, kErrMmaWaitTmem, (uint32_t)local_tile);
           ok = false;
           break;
         }
+        TB200_PROF_ADD(prof_wtmem, tw0);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
         for (int it = 0; it < k_iters; ++it) {
-          if (!mbar_try_wait(full_addr, phase) &&
-              !mbar_wait_bounded(full_addr, phase, abort_p, kWaitLimitCycles)) {
+          TB200_PROF_T(tw1);
+          if (!stage_ready && !mbar_wait_bounded(full_addr, phase, abort_p, kWaitLimitCycles)) {
             report_error(args, abort_p, kErrMmaWaitFull, (uint32_t)it);
             ok = false;
             break;
           }
+          TB200_PROF_ADD(prof_wfull, tw1);
+          // probe the next stage now; the MMAs below are issued while the answer is on its way
+          uint32_t n_off = s_off + kStageUnits, nfull = full_addr + 8u, nempty = empty_addr + 8u, nphase = phase;
+          if (n_off == ring_units) { n_off = 0; nfull = full_bar0; nempty = empty_bar0; nphase ^= 1u; }
           tc_fence_after();
-          if (it == 0) mma_ss_lean<kTf32, false>(d_tmem, a_k[0] + s_off, b_k[0] + s_off, desc_hi, idesc);
-          else mma_ss_lean<kTf32, true>(d_tmem, a_k[0] + s_off, b_k[0] + s_off, desc_hi, idesc);
-          mma_ss_lean<kTf32, true>(d_tmem, a_k[1] + s_off, b_k[1] + s_off, desc_hi, idesc);
-          mma_ss_lean<kTf32, true>(d_tmem, a_k[2] + s_off, b_k[2] + s_off, desc_hi, idesc);
-          mma_ss_lean<kTf32, true>(d_tmem, a_k[3] + s_off, b_k[3] + s_off, desc_hi, idesc);
-          mma_commit(empty_addr);                 // stage reusable once these MMAs retire
-          s_off += kStageUnits; full_addr += 8u; empty_addr += 8u;
-          if (s_off == ring_units) { s_off = 0; full_addr = full_bar0; empty_addr = empty_bar0; phase ^= 1u; }
+          bool next_ready;
+          if (it == 0)
+            next_ready = mma_stage4_probe<kTf32, false>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
+                                                        a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off,
+                                                        b_k[3] + s_off, desc_hi, idesc, empty_addr, nfull, nphase);
+          else
+            next_ready = mma_stage4_probe<kTf32, true>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
+                                                       a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off,
+                                                       b_k[3] + s_off, desc_hi, idesc, empty_addr, nfull, nphase);
+          s_off = n_off; full_addr = nfull; empty_addr = nempty; phase = nphase;
+          stage_ready = next_ready;
         }
         if (ok) mma_commit(tfull_bar(buf));       // accumulator complete
       }
+      TB200_PROF_STORE(2, prof_wfull);
+      TB200_PROF_STORE(3, prof_wtmem);
+      TB200_PROF_STORE(4, clock64() - prof_t0);
     }
   } else {
     // ------------------------------------------------------------ epilogue warps (2..5)
@@ -436,6 +510,9 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (static_cast<int>(blockIdx.x) < num_tiles) fetch_bias(static_cast<int>(blockIdx.x) % args.num_n_tiles);
     int local_tile = 0;
     bool ok = true;
+    long long prof_wacc = 0, prof_wres = 0, prof_ld = 0, prof_math = 0, prof_stage = 0, prof_wstore = 0;
+    (void)prof_wacc; (void)prof_wres; (void)prof_ld; (void)prof_math; (void)prof_stage; (void)prof_wstore;
+    TB200_PROF_T(prof_t0);
     int m_tile = first_m_tile - tile_step_m, n_tile = first_n_tile - tile_step_n;
     const bool need_coords = !args.out_tma || (res != nullptr && !res_tma);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -485,7 +562,9 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
       }
 
+      TB200_PROF_T(tw2);
       const bool ready = mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_p, kWaitLimitCycles);
+      TB200_PROF_ADD(prof_wacc, tw2);
       if (!__all_sync(0xffffffffu, ready)) {      // keep the warp converged for tcgen05.ld
         if (lane == 0) report_error(args, abort_p, kErrEpilogueWait, (uint32_t)local_tile);
         ok = false;
@@ -495,7 +574,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t taddr0 =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
 
-#pragma unroll
+#pragma unroll 1
       for (int g = 0; g < kGroups; ++g) {
         const int n0 = n_base + g * kGroupCols;
         const bool group_live = n0 < args.K_out;   // warp-uniform: false when the group is past K_out
@@ -511,9 +590,11 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
         }
         uint32_t v[kLdPerGroup][32];
+        TB200_PROF_T(tl);
 #pragma unroll
         for (int h = 0; h < kLdPerGroup; ++h) tmem_ld_32x32(taddr0 + g * kGroupCols + h * 32, v[h]);
         tmem_ld_wait();
+        TB200_PROF_ADD(prof_ld, tl);
         if (g == kGroups - 1) {
           // the accumulator is in registers now: hand the TMEM buffer back to the MMA issuer
           tc_fence_before();
@@ -523,8 +604,10 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (!group_live) continue;
 
         if (res_tma) {
+          TB200_PROF_T(tw3);
           const bool landed = mbar_wait_bounded(res_bar(quarter, box), (box_phase >> box) & 1u, abort_p,
                                                 kWaitLimitCycles);
+          TB200_PROF_ADD(prof_wres, tw3);
           if (!__all_sync(0xffffffffu, landed)) {
             if (lane == 0) report_error(args, abort_p, kErrResidualWait, (uint32_t)local_tile);
             ok = false;
@@ -532,10 +615,13 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
           box_phase ^= (1u << box);
         } else if (args.out_tma) {
+          TB200_PROF_T(ts);
           if (lane == 0) bulk_wait_group_read<2>();   // this box's previous store has been read out
           __syncwarp();
+          TB200_PROF_ADD(prof_wstore, ts);
         }
 
+        TB200_PROF_T(tm);
         uint4 packed[8];
 #pragma unroll
         for (int h = 0; h < kLdPerGroup; ++h) {
@@ -548,40 +634,28 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             f[j4 * 4 + 2] = __uint_as_float(v[h][j4 * 4 + 2]) + b4.z;
             f[j4 * 4 + 3] = __uint_as_float(v[h][j4 * 4 + 3]) + b4.w;
           }
-          if (res != nullptr) {
-            if (res_tma) {
+          if (!args.out_tma) {
+            float fg[32];   // a copy the out-of-line path may keep in local memory; f stays in registers
 #pragma unroll
-              for (int c = 0; c < kChunksPerLd; ++c) {
-                const uint32_t cc = static_cast<uint32_t>(h * kChunksPerLd + c);
-                add16<OutT>(f + c * kVec, ld_shared_v4(stg + lane_row_off + ((cc ^ lane_xor) << 4)));
-              }
-            } else if (row_ok) {
-              if (args.res_vec) {
+            for (int j = 0; j < 32; ++j) fg[j] = f[j];
+            epilogue_block_generic<OutT>(
+                args, fg, res != nullptr ? res_row + static_cast<long long>(g * kGroupCols + h * 32) * args.res_sc : nullptr,
+                out + out_off + static_cast<long long>(n0 + h * 32) * args.out_sc, n0 + h * 32, row_ok);
+            continue;
+          }
+          if (res_tma) {   // with TMA output a residual is always TMA-loaded (the host guarantees it)
 #pragma unroll
-                for (int c = 0; c < kChunksPerLd; ++c)
-                  if (n0 + h * 32 + c * kVec < args.K_out)
-                    add16<OutT>(f + c * kVec,
-                                __ldg(reinterpret_cast<const uint4*>(res_row + g * kGroupCols + h * 32) + c));
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (n0 + h * 32 + j < args.K_out)
-                    f[j] += OutTraits<OutT>::to_f(res_row[(g * kGroupCols + h * 32 + j) * args.res_sc]);
-              }
+            for (int c = 0; c < kChunksPerLd; ++c) {
+              const uint32_t cc = static_cast<uint32_t>(h * kChunksPerLd + c);
+              add16<OutT>(f + c * kVec, ld_shared_v4(stg + lane_row_off + ((cc ^ lane_xor) << 4)));
             }
           }
           apply_act32<sizeof(OutT) == 2>(f, args.act);
-          if (args.out_tma || args.out_vec) {
 #pragma unroll
-            for (int c = 0; c < kChunksPerLd; ++c) packed[h * kChunksPerLd + c] = pack16<OutT>(f + c * kVec);
-          } else if (row_ok) {
-            // lanes are consecutive pixels: for NCHW memory (sw == 1) each store instruction is coalesced
-            OutT* op = out + out_off + static_cast<long long>(n0 + h * 32) * args.out_sc;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n0 + h * 32 + j < args.K_out) op[j * args.out_sc] = OutTraits<OutT>::from_f(f[j]);
-          }
+          for (int c = 0; c < kChunksPerLd; ++c) packed[h * kChunksPerLd + c] = pack16<OutT>(f + c * kVec);
         }
+        TB200_PROF_ADD(prof_math, tm);
+        TB200_PROF_T(tg);
         if (args.out_tma) {
           // the lane's pixel row goes to its swizzled 128-byte row of the box; one TMA store writes the box
 #pragma unroll
@@ -594,15 +668,20 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             bulk_commit_group();
           }
           box = (box + 1u) % kStagingDepth;
-        } else if (args.out_vec && row_ok) {
-          OutT* op = out + out_off + static_cast<long long>(n0) * args.out_sc;
-#pragma unroll
-          for (int c = 0; c < 8; ++c)
-            if (n0 + c * kVec < args.K_out) reinterpret_cast<uint4*>(op)[c] = packed[c];
         }
+        TB200_PROF_ADD(prof_stage, tg);
       }
     }
     if (args.out_tma && lane == 0) bulk_wait_group0();
+    if (warp == 2 && lane == 0) {
+      TB200_PROF_STORE(5, prof_wacc);
+      TB200_PROF_STORE(6, prof_wres);
+      TB200_PROF_STORE(7, clock64() - prof_t0);
+      TB200_PROF_STORE(8, prof_ld);
+      TB200_PROF_STORE(9, prof_math);
+      TB200_PROF_STORE(10, prof_stage);
+      TB200_PROF_STORE(11, prof_wstore);
+    }
   }
 
   // ---------------------------------------------------------------- teardown

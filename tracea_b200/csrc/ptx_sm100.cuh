@@ -58,6 +58,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe. Its result takes a couple of hundred cycles to come back, so the single-thread
+// roles issue the probe for the NEXT stage before working on the current one and only read the
+// answer afterwards.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. `abort_flag` is a CTA-shared word any role sets when it gives up; every waiter
 // polls it so that one failed wait unwinds the whole CTA. `limit_cycles` bounds this wait alone.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
@@ -227,6 +244,80 @@ __device__ __forceinline__ void mma_ss_lean(uint32_t tmem_d, uint32_t a_lo, uint
         : "memory");
   }
 }
+// One pipeline stage of the MMA issuer as a single block: probe the NEXT stage's full barrier, issue
+// the four MMAs of this stage, commit them to this stage's empty barrier, and only then read the
+// probe's predicate -- so the probe's latency is spent under the MMA issue instead of stalling the
+// in-order thread in front of it. Returns whether the next stage was already full.
+template <bool kTf32, bool kFirstAccumulates>
+__device__ __forceinline__ bool mma_stage4_probe(uint32_t tmem_d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3,
+                                                 uint32_t desc_hi, uint32_t idesc, uint32_t empty_bar,
+                                                 uint32_t next_full_bar, uint32_t next_parity) {
+  uint32_t ready;
+#define TB200_MMA_STAGE(KIND)                                                                   \
+  asm volatile(                                                                                  \
+      "{\n"                                                                                      \
+      ".reg .pred pn, p0, p1;\n"                                                                 \
+      ".reg .b64 da, db;\n"                                                                      \
+      "mbarrier.test_wait.parity.shared::cta.b64 pn, [%13], %14;\n"                              \
+      "setp.ne.b32 p0, %15, 0;\n"                                                                \
+      "setp.eq.b32 p1, 0, 0;\n"                                                                  \
+      "mov.b64 da, {%2, %10};\n"                                                                 \
+      "mov.b64 db, {%6, %10};\n"                                                                 \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%1], da, db, %11, p0;\n"                         \
+      "mov.b64 da, {%3, %10};\n"                                                                 \
+      "mov.b64 db, {%7, %10};\n"                                                                 \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%1], da, db, %11, p1;\n"                         \
+      "mov.b64 da, {%4, %10};\n"                                                                 \
+      "mov.b64 db, {%8, %10};\n"                                                                 \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%1], da, db, %11, p1;\n"                         \
+      "mov.b64 da, {%5, %10};\n"                                                                 \
+      "mov.b64 db, {%9, %10};\n"                                                                 \
+      "tcgen05.mma.cta_group::1.kind::" KIND " [%1], da, db, %11, p1;\n"                         \
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%12];\n"           \
+      "selp.u32 %0, 1, 0, pn;\n"                                                                 \
+      "}\n"                                                                                      \
+      : "=r"(ready)                                                                              \
+      : "r"(tmem_d), "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(b2), "r"(b3),     \
+        "r"(desc_hi), "r"(idesc), "r"(empty_bar), "r"(next_full_bar), "r"(next_parity),          \
+        "n"(kFirstAccumulates ? 1 : 0)                                                           \
+      : "memory")
+  if constexpr (kTf32) {
+    TB200_MMA_STAGE("tf32");
+  } else {
+    TB200_MMA_STAGE("f16");
+  }
+#undef TB200_MMA_STAGE
+  return ready != 0;
+}
+
+// One pipeline stage of the TMA producer as a single block, same idea: probe the NEXT slot's empty
+// barrier first, then arm this slot's full barrier and issue the im2col copy of A and the tiled copy
+// of B, then read the probe.
+__device__ __forceinline__ bool tma_stage_probe(uint32_t a_dst, uint32_t b_dst, uint32_t full_bar, uint32_t stage_bytes,
+                                                const void* tmap_x, int c, int w, int h, int n, uint16_t off_w,
+                                                uint16_t off_h, const void* tmap_w, int k0, int n0,
+                                                uint32_t next_empty_bar, uint32_t next_parity) {
+  uint32_t free_next;
+  asm volatile(
+      "{\n"
+      ".reg .pred pn;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 pn, [%15], %16;\n"
+      "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%3], %4;\n"
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+      " [%1], [%5, {%6, %7, %8, %9}], [%3], {%10, %11};\n"
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%2], [%12, {%13, %14}], [%3];\n"
+      "selp.u32 %0, 1, 0, pn;\n"
+      "}\n"
+      : "=r"(free_next)
+      : "r"(a_dst), "r"(b_dst), "r"(full_bar), "r"(stage_bytes), "l"(reinterpret_cast<uint64_t>(tmap_x)), "r"(c),
+        "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h), "l"(reinterpret_cast<uint64_t>(tmap_w)), "r"(k0), "r"(n0),
+        "r"(next_empty_bar), "r"(next_parity)
+      : "memory");
+  return free_next != 0;
+}
+
 // Arrive on `bar` once every tcgen05.mma issued so far by this thread has retired.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(

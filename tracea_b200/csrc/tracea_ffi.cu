@@ -692,10 +692,18 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS) TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled (residual) failed with %d", (int)r);
       a.res_tma = 1;
+    } else {
+      a.out_tma = 0;   // the kernel's TMA epilogue takes its residual through TMA or not at all
     }
   }
   a.act = epi.act;
   a.status = st.status;
+#ifdef TB200_PROFILE
+  {  // bring-up builds only: TRACEA_B200_PROF_PTR carries a device pointer to 8 counters per CTA
+    const char* pp = getenv("TRACEA_B200_PROF_PTR");
+    a.prof = pp != nullptr ? reinterpret_cast<long long*>(strtoull(pp, nullptr, 0)) : nullptr;
+  }
+#endif
 
   const long long tiles = m_tiles * n_tiles;
   const int grid = static_cast<int>(std::min<long long>(tiles, st.num_sms));
