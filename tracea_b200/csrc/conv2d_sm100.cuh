@@ -90,16 +90,19 @@ struct ConvKernelArgs {
 template <typename T> struct OutTraits;
 template <> struct OutTraits<__nv_bfloat16> {
   static constexpr bool kTf32 = false;
+  static constexpr bool kIsBf16 = true;
   __device__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
   __device__ static __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
 template <> struct OutTraits<__half> {
   static constexpr bool kTf32 = false;
+  static constexpr bool kIsBf16 = false;
   __device__ static float to_f(__half v) { return __half2float(v); }
   __device__ static __half from_f(float v) { return __float2half_rn(v); }
 };
 template <> struct OutTraits<float> {
   static constexpr bool kTf32 = true;
+  static constexpr bool kIsBf16 = false;
   __device__ static float to_f(float v) { return v; }
   __device__ static float from_f(float v) { return v; }
 };
@@ -168,6 +171,85 @@ __device__ __forceinline__ uint4 pack16(const float* f) {
     for (int j = 0; j < 8; ++j) e[j] = OutTraits<OutT>::from_f(f[j]);
   }
   return r;
+}
+
+// (a, b) += (c, d) as one packed fp32x2 add.
+__device__ __forceinline__ void add2(float& a, float& b, float c, float d) {
+  asm("{\n"
+      ".reg .b64 x, y;\n"
+      "mov.b64 x, {%0, %1};\n"
+      "mov.b64 y, {%2, %3};\n"
+      "add.rn.f32x2 x, x, y;\n"
+      "mov.b64 {%0, %1}, x;\n"
+      "}\n"
+      : "+f"(a), "+f"(b)
+      : "f"(c), "f"(d));
+}
+
+// Two consecutive fp32 values -> one packed word of the 16-bit output type (element 0 in the low
+// half), optionally with ReLU folded into the conversion instruction.
+template <typename OutT, bool kRelu>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  uint32_t r;
+  if constexpr (sizeof(OutT) == 2 && OutTraits<OutT>::kIsBf16) {
+    if constexpr (kRelu) asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  } else {
+    if constexpr (kRelu) asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  }
+  return r;
+}
+
+// One packed word of the 16-bit type -> two fp32 values.
+template <typename OutT>
+__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi) {
+  if constexpr (OutTraits<OutT>::kIsBf16) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+}
+
+// 32 fp32 values (acc + bias [+ residual from 16-byte chunks]) -> packed output chunks, for the TMA
+// epilogue. 16-bit outputs: kChunks = 4 chunks of 8; fp32 outputs: 8 chunks of 4.
+template <typename OutT, bool kRelu>
+__device__ __forceinline__ void finish32(float (&f)[32], const uint4* res_chunks, bool has_res, uint4* packed) {
+  if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (has_res) {
+        const uint4 r = res_chunks[c];
+        float lo, hi;
+        unpack2<OutT>(r.x, lo, hi); add2(f[c * 8 + 0], f[c * 8 + 1], lo, hi);
+        unpack2<OutT>(r.y, lo, hi); add2(f[c * 8 + 2], f[c * 8 + 3], lo, hi);
+        unpack2<OutT>(r.z, lo, hi); add2(f[c * 8 + 4], f[c * 8 + 5], lo, hi);
+        unpack2<OutT>(r.w, lo, hi); add2(f[c * 8 + 6], f[c * 8 + 7], lo, hi);
+      }
+      packed[c].x = pack2<OutT, kRelu>(f[c * 8 + 0], f[c * 8 + 1]);
+      packed[c].y = pack2<OutT, kRelu>(f[c * 8 + 2], f[c * 8 + 3]);
+      packed[c].z = pack2<OutT, kRelu>(f[c * 8 + 4], f[c * 8 + 5]);
+      packed[c].w = pack2<OutT, kRelu>(f[c * 8 + 6], f[c * 8 + 7]);
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      if (has_res) {
+        const uint4 r = res_chunks[c];
+        add2(f[c * 4 + 0], f[c * 4 + 1], __uint_as_float(r.x), __uint_as_float(r.y));
+        add2(f[c * 4 + 2], f[c * 4 + 3], __uint_as_float(r.z), __uint_as_float(r.w));
+      }
+      if constexpr (kRelu) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) f[c * 4 + j] = fmaxf(0.0f, f[c * 4 + j]);
+      }
+      packed[c] = make_uint4(__float_as_uint(f[c * 4 + 0]), __float_as_uint(f[c * 4 + 1]),
+                             __float_as_uint(f[c * 4 + 2]), __float_as_uint(f[c * 4 + 3]));
+    }
+  }
 }
 
 template <typename OutT>
@@ -627,12 +709,12 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         for (int h = 0; h < kLdPerGroup; ++h) {
           float f[32];
 #pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[h][j]);
+#pragma unroll
           for (int j4 = 0; j4 < 8; ++j4) {
             const float4 b4 = ld_shared_f4(bias_w_s + static_cast<uint32_t>(g * kGroupCols + h * 32 + j4 * 4) * 4u);
-            f[j4 * 4 + 0] = __uint_as_float(v[h][j4 * 4 + 0]) + b4.x;
-            f[j4 * 4 + 1] = __uint_as_float(v[h][j4 * 4 + 1]) + b4.y;
-            f[j4 * 4 + 2] = __uint_as_float(v[h][j4 * 4 + 2]) + b4.z;
-            f[j4 * 4 + 3] = __uint_as_float(v[h][j4 * 4 + 3]) + b4.w;
+            add2(f[j4 * 4 + 0], f[j4 * 4 + 1], b4.x, b4.y);
+            add2(f[j4 * 4 + 2], f[j4 * 4 + 3], b4.z, b4.w);
           }
           if (!args.out_tma) {
             float fg[32];   // a copy the out-of-line path may keep in local memory; f stays in registers
@@ -643,16 +725,26 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 out + out_off + static_cast<long long>(n0 + h * 32) * args.out_sc, n0 + h * 32, row_ok);
             continue;
           }
-          if (res_tma) {   // with TMA output a residual is always TMA-loaded (the host guarantees it)
+          // TMA output; a residual, if any, sits in this lane's row of the staging box (the host
+          // guarantees a residual is TMA-loaded whenever the output is TMA-stored)
+          uint4 rchunks[kChunksPerLd];
+          if (res_tma) {
 #pragma unroll
             for (int c = 0; c < kChunksPerLd; ++c) {
               const uint32_t cc = static_cast<uint32_t>(h * kChunksPerLd + c);
-              add16<OutT>(f + c * kVec, ld_shared_v4(stg + lane_row_off + ((cc ^ lane_xor) << 4)));
+              rchunks[c] = ld_shared_v4(stg + lane_row_off + ((cc ^ lane_xor) << 4));
             }
           }
-          apply_act32<sizeof(OutT) == 2>(f, args.act);
+          if (args.act == kActRelu) {
+            finish32<OutT, true>(f, rchunks, res_tma, packed + h * kChunksPerLd);
+          } else {
+            if (res_tma) {
 #pragma unroll
-          for (int c = 0; c < kChunksPerLd; ++c) packed[h * kChunksPerLd + c] = pack16<OutT>(f + c * kVec);
+              for (int c = 0; c < kChunksPerLd; ++c) add16<OutT>(f + c * kVec, rchunks[c]);
+            }
+            apply_act32<sizeof(OutT) == 2>(f, args.act);
+            finish32<OutT, false>(f, rchunks, false, packed + h * kChunksPerLd);
+          }
         }
         TB200_PROF_ADD(prof_math, tm);
         TB200_PROF_T(tg);

@@ -575,7 +575,8 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     CUresult r = g_encode_im2col(&tmap_x, tmap_dtype(x.dtype), 4, x.ptr, gdim, gstr, lower, upper,
                                  (cuuint32_t)chunk_elems, (cuuint32_t)tb200::kBlockM, estr,
                                  CU_TENSOR_MAP_INTERLEAVE_NONE, tmap_swizzle(chunk_bytes),
-                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
       TB_FAIL(TRACEA_CUDA_ERROR,
               "cuTensorMapEncodeIm2col failed with %d (C=%lld W=%lld H=%lld N=%lld chunk=%d B lower=(%d,%d) "
