@@ -281,6 +281,11 @@ EDGE = [
     (1, 32, 23, 23, 32, 3, 3, 3, 4, 2, "gelu"),            # stride 3, large padding, dilation 2
     (1, 64, 32, 32, 64, 7, 7, 2, 3, 1, "bias+relu"),       # 7x7 / 2
     (5, 64, 7, 7, 2048, 1, 1, 1, 0, 1, "bias+relu"),       # wide output, tiny image
+    (2, 3, 37, 41, 64, 7, 7, 2, 3, 1, "bias+relu"),        # RGB stem: 16-byte pixels, filter rows fetched as windows
+    (2, 8, 20, 30, 16, 2, 8, (1, 2), (0, 3), 1, ""),       # 8-wide filter row fills the whole window
+    (2, 8, 20, 30, 16, 3, 9, 1, (1, 4), 1, ""),            # 9-wide filter: too wide for a window, per-tap path
+    (2, 8, 21, 21, 16, 3, 3, 1, 2, (1, 2), "silu"),        # 16-byte pixels with horizontal dilation: per-tap path
+    (1, 4, 9, 200, 8, 1, 5, 1, (0, 2), 1, "bias"),         # one-row filter on a wide image
 ]
 
 

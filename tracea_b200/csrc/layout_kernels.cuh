@@ -44,21 +44,50 @@ __global__ void to_channels_last_kernel(const T* __restrict__ src, T* __restrict
   }
 }
 
+// Small-channel inputs (one pixel = 16 bytes after channel padding, e.g. RGB as 8 x bf16): x -> dst[n][h][Wp][Cp]
+// with `pad` zero pixels in front of every row and zeros up to the row pitch Wp behind it. With the
+// horizontal padding materialised, the S taps of one filter row are adjacent in memory, so the conv
+// kernel fetches a whole filter row of a pixel (8 pixels x 16 B = one 128-byte k-chunk) with one copy.
+// One thread writes one destination pixel (16 bytes).
+template <typename T, int kCp>
+__global__ void to_channels_last_wpad_kernel(const T* __restrict__ src, T* __restrict__ dst, int C, int H, int W,
+                                             int Wp, int pad, long long total_pixels, long long sn, long long sc,
+                                             long long sh, long long sw) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= total_pixels) return;
+  const int wp = static_cast<int>(i % Wp);
+  const long long t = i / Wp;
+  const int h = static_cast<int>(t % H);
+  const long long n = t / H;
+  const int w = wp - pad;
+  T v[kCp];
+#pragma unroll
+  for (int c = 0; c < kCp; ++c) v[c] = T(0);
+  if (w >= 0 && w < W) {
+    const T* p = src + n * sn + h * sh + w * sw;
+#pragma unroll
+    for (int c = 0; c < kCp; ++c)
+      if (c < C) v[c] = p[c * sc];
+  }
+  *reinterpret_cast<uint4*>(dst + i * kCp) = *reinterpret_cast<const uint4*>(v);
+}
+
 // w[k, c, r, s] (element strides) -> dst[k][r][s][Cp], zero-padded channels: the K-major B operand
 // whose Kgemm axis runs (r, s, c), the order the reference walks it (conv.rs:209-210).
+// `Sd` >= S is the number of tap slots per filter row in the destination (slots s >= S are zero).
 template <typename T>
 __global__ void pack_weights_krsc_kernel(const T* __restrict__ src, T* __restrict__ dst,
-                                         long long total, int C, int R, int S, int Cp, long long sk,
+                                         long long total, int C, int R, int S, int Sd, int Cp, long long sk,
                                          long long sc, long long sr, long long ss) {
   const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (i >= total) return;
   const int c = static_cast<int>(i % Cp);
   long long t = i / Cp;
-  const int s = static_cast<int>(t % S);
-  t /= S;
+  const int s = static_cast<int>(t % Sd);
+  t /= Sd;
   const int r = static_cast<int>(t % R);
   const long long k = t / R;
-  dst[i] = (c < C) ? src[k * sk + c * sc + r * sr + s * ss] : T(0);
+  dst[i] = (c < C && s < S) ? src[k * sk + c * sc + r * sr + s * ss] : T(0);
 }
 
 }  // namespace tb200

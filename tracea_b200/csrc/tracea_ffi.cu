@@ -464,13 +464,39 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   const int vec_elems = 16 / es;
   const long long Cp = (C + vec_elems - 1) / vec_elems * vec_elems;
 
+  // ---- small-channel inputs (a pixel is 16 bytes after channel padding, e.g. the RGB stem): copy x with the
+  // horizontal padding materialised; one filter row of a pixel is then 8 adjacent pixels = one 128-byte
+  // k-chunk, fetched by a single im2col copy over an overlapping view (pixel pitch 16 B, "pixel" size 128 B).
+  const bool window = Cp * es == 16 && S > 1 && S <= 8 && p.dilation_w == 1 && W + 2LL * p.padding_w < (1LL << 30) &&
+                      env_int("TRACEA_B200_NO_WINDOW", 0) == 0;
+  const long long Wpitch = W + 2LL * p.padding_w + 8;   // row pitch of the padded copy, in pixels
+
   // ---- activations: consume channels-last memory directly, otherwise transpose into scratch
   View4 x = x_in;
   Scratch x_scratch;
   const bool x_direct = x.stride[1] == 1 && C == Cp && aligned16(x.ptr) &&
                         (x.stride[3] * es) % 16 == 0 && (x.stride[2] * es) % 16 == 0 &&
                         (x.stride[0] * es) % 16 == 0 && x.stride[3] >= C;
-  if (!x_direct || env_int("TRACEA_B200_FORCE_STAGING", 0)) {
+  if (window) {
+    const long long pixels = N * H * Wpitch;
+    void* x_stage = staging(x_scratch, static_cast<size_t>(pixels * Cp) * es, "the padded channels-last copy of x");
+    const int threads = 256;
+    const unsigned blocks = static_cast<unsigned>((pixels + threads - 1) / threads);
+    if (es == 2)
+      tb200::to_channels_last_wpad_kernel<uint16_t, 8><<<blocks, threads, 0, stream>>>(
+          static_cast<const uint16_t*>(x.ptr), static_cast<uint16_t*>(x_stage), (int)C, (int)H, (int)W, (int)Wpitch,
+          (int)p.padding_w, pixels, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
+    else
+      tb200::to_channels_last_wpad_kernel<uint32_t, 4><<<blocks, threads, 0, stream>>>(
+          static_cast<const uint32_t*>(x.ptr), static_cast<uint32_t*>(x_stage), (int)C, (int)H, (int)W, (int)Wpitch,
+          (int)p.padding_w, pixels, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
+    TB_CUDA(cudaGetLastError());
+    x.ptr = x_stage;
+    x.stride[0] = H * Wpitch * Cp;
+    x.stride[1] = 1;
+    x.stride[2] = Wpitch * Cp;
+    x.stride[3] = Cp;
+  } else if (!x_direct || env_int("TRACEA_B200_FORCE_STAGING", 0)) {
     void* x_stage = staging(x_scratch, static_cast<size_t>(N * H * W * Cp) * es, "the channels-last copy of x");
     dim3 grid(static_cast<unsigned>((H * W + 31) / 32), static_cast<unsigned>((Cp + 31) / 32),
               static_cast<unsigned>(N));
@@ -498,25 +524,29 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   Scratch w_scratch;
   const bool w_direct = C == Cp && (w_in.stride[1] == 1) && w_in.stride[3] == C &&
                         w_in.stride[2] == S * C && w_in.stride[0] == R * S * C && aligned16(w_in.ptr);
-  if (!w_direct) {
-    const long long total = K * R * S * Cp;
+  const long long Sd = window ? 8 : S;   // tap slots per filter row in the packed weights
+  if (!w_direct || window) {
+    const long long total = K * R * Sd * Cp;
     void* w_stage = staging(w_scratch, static_cast<size_t>(total) * es, "the repacked weights");
     const int threads = 256;
     const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
     if (es == 2)
       tb200::pack_weights_krsc_kernel<uint16_t><<<blocks, threads, 0, stream>>>(
           static_cast<const uint16_t*>(w_in.ptr), static_cast<uint16_t*>(w_stage), total, (int)C,
-          (int)R, (int)S, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
+          (int)R, (int)S, (int)Sd, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
     else
       tb200::pack_weights_krsc_kernel<uint32_t><<<blocks, threads, 0, stream>>>(
           static_cast<const uint32_t*>(w_in.ptr), static_cast<uint32_t*>(w_stage), total, (int)C,
-          (int)R, (int)S, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
+          (int)R, (int)S, (int)Sd, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
     TB_CUDA(cudaGetLastError());
     w_ptr = w_stage;
   }
 
   // ---- k-chunking: the widest power-of-two row (<= 128 B) that divides one pixel's channels
-  const long long row_bytes = Cp * es;
+  // In window mode the kernel sees a conv with one tap per filter row over "pixels" of 8 * Cp channels.
+  const long long Cg = window ? 8 * Cp : Cp;      // channel extent of the kernel's view
+  const long long Sg = window ? 1 : S;            // taps per filter row of the kernel's view
+  const long long row_bytes = Cg * es;
   int chunk_bytes = 16;
   for (int cb = 128; cb >= 16; cb >>= 1) {
     if (row_bytes % cb == 0) {
@@ -529,10 +559,10 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     if (row_bytes % forced_chunk == 0) chunk_bytes = forced_chunk;
   }
   const int chunk_elems = chunk_bytes / es;
-  const int chunks_per_tap = static_cast<int>(Cp / chunk_elems);
-  const long long total_chunks_ll = R * S * chunks_per_tap;
+  const int chunks_per_tap = static_cast<int>(Cg / chunk_elems);
+  const long long total_chunks_ll = R * Sg * chunks_per_tap;
   if (total_chunks_ll > 0x7fffffffLL / 128) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "R*S*C too large");
-  const long long Kgemm = R * S * Cp;
+  const long long Kgemm = R * Sg * Cg;
 
   // ---- tiles
   const long long m_tiles = (M + tb200::kBlockM - 1) / tb200::kBlockM;
@@ -552,7 +582,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   memset(&tmap_res, 0, sizeof(tmap_res));
   // A 1x1 / stride-1 / unpadded conv over dense NHWC memory is a plain [M][C] x [C][K] GEMM; the
   // tiled map is kept as a cross-check of the im2col path (TRACEA_B200_TILED_A=1).
-  const bool a_tiled = env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
+  const bool a_tiled = !window && env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
                        p.stride_w == 1 && p.padding_h == 0 && p.padding_w == 0 && x.stride[3] == Cp &&
                        x.stride[2] == W * Cp && x.stride[0] == H * W * Cp;
   if (a_tiled) {
@@ -565,11 +595,14 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled (A) failed with %d", (int)r);
   } else {
-    const cuuint64_t gdim[4] = {(cuuint64_t)Cp, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    // window mode: "pixel" w of the view starts at padded pixel w and spans 8 of them (pitch 16 B, extent
+    // 128 B, overlapping); the horizontal padding is in memory, so the W corners only trim the filter width
+    const cuuint64_t gdim[4] = {(cuuint64_t)Cg, (cuuint64_t)(window ? W + 2LL * p.padding_w : W), (cuuint64_t)H,
+                                (cuuint64_t)N};
     const cuuint64_t gstr[3] = {(cuuint64_t)(x.stride[3] * es), (cuuint64_t)(x.stride[2] * es),
                                 (cuuint64_t)(x.stride[0] * es)};
-    const int lower[2] = {-(int)p.padding_w, -(int)p.padding_h};
-    const int upper[2] = {(int)p.padding_w - (int)((S - 1) * p.dilation_w),
+    const int lower[2] = {window ? 0 : -(int)p.padding_w, -(int)p.padding_h};
+    const int upper[2] = {window ? -(int)(S - 1) : (int)p.padding_w - (int)((S - 1) * p.dilation_w),
                           (int)p.padding_h - (int)((R - 1) * p.dilation_h)};
     const cuuint32_t estr[4] = {1u, p.stride_w, p.stride_h, 1u};
     CUresult r = g_encode_im2col(&tmap_x, tmap_dtype(x.dtype), 4, x.ptr, gdim, gstr, lower, upper,
@@ -581,7 +614,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
       TB_FAIL(TRACEA_CUDA_ERROR,
               "cuTensorMapEncodeIm2col failed with %d (C=%lld W=%lld H=%lld N=%lld chunk=%d B lower=(%d,%d) "
               "upper=(%d,%d) stride=(%u,%u))",
-              (int)r, Cp, W, H, N, chunk_bytes, lower[0], lower[1], upper[0], upper[1], p.stride_w,
+              (int)r, Cg, W, H, N, chunk_bytes, lower[0], lower[1], upper[0], upper[1], p.stride_w,
               p.stride_h);
   }
   {
@@ -607,15 +640,15 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   a.stride_h = p.stride_h;
   a.stride_w = p.stride_w;
   a.pad_h = p.padding_h;
-  a.pad_w = p.padding_w;
+  a.pad_w = window ? 0 : p.padding_w;
   a.dil_h = p.dilation_h;
   a.dil_w = p.dilation_w;
-  a.S = static_cast<int>(S);
+  a.S = static_cast<int>(Sg);
   a.chunk_elems = chunk_elems;
   a.chunk_bytes = chunk_bytes;
   a.chunks_per_tap = chunks_per_tap;
   a.total_chunks = static_cast<int>(total_chunks_ll);
-  a.C = static_cast<int>(Cp);
+  a.C = static_cast<int>(Cg);
   a.a_tiled = a_tiled ? 1 : 0;
   a.num_m_tiles = static_cast<int>(m_tiles);
   a.num_n_tiles = static_cast<int>(n_tiles);
