@@ -30,7 +30,7 @@ namespace tb200 {
 
 constexpr int kBlockM = 128;          // output pixels per tile = TMEM lanes
 constexpr int kStageKBytes = 128;     // bytes of K per smem row per pipeline stage
-constexpr int kNumThreads = 192;      // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int kNumThreads = 320;      // warp 0 TMA, warp 1 MMA, warps 2..5 and 6..9 two epilogue groups
 constexpr int kMaxStages = 12;
 constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 1.9 GHz, per wait
 
@@ -147,15 +147,16 @@ __device__ __forceinline__ void report_error(const ConvKernelArgs& a, volatile u
 
 // Shared memory map (offsets from a 1024-byte aligned base):
 //   [0, stages * stage_bytes)        operand ring: per stage A (128 rows x 128 B) then B (BN rows x 128 B)
-//   + kStagingBytes                  per epilogue warp 3 rotating 4 KB boxes (32 pixels x 128 B): the residual
+//   + kStagingBytes                  per epilogue warp 2 alternating 4 KB boxes (32 pixels x 128 B): the residual
 //                                    is TMA-loaded into a box, combined in place, and the box is TMA-stored
-//   + 4 * BN * 4                     per-epilogue-warp copy of the tile's bias, as fp32
+//   + 8 * BN * 4                     per-epilogue-warp copy of the tile's bias, as fp32
 //   + 256                            mbarriers, TMEM base slot, abort flag
 constexpr int kStagingBoxBytes = 32 * 128;
-constexpr int kStagingDepth = 3;
-constexpr int kStagingBytes = 4 * kStagingDepth * kStagingBoxBytes;
+constexpr int kStagingDepth = 2;
+constexpr int kNumEpilogueWarps = 8;
+constexpr int kStagingBytes = kNumEpilogueWarps * kStagingDepth * kStagingBoxBytes;
 __host__ __device__ constexpr int conv_smem_bytes(int bn, int stages) {
-  return stages * (kBlockM * kStageKBytes + bn * kStageKBytes) + kStagingBytes + 4 * bn * 4 + 512 + 1024;
+  return stages * (kBlockM * kStageKBytes + bn * kStageKBytes) + kStagingBytes + kNumEpilogueWarps * bn * 4 + 512 + 1024;
 }
 
 // 8 consecutive fp32 values -> one 16-byte vector of OutT (16-bit types) / 4 values (fp32).
@@ -314,14 +315,14 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t ring_bytes = static_cast<uint32_t>(num_stages) * kStageBytes;
   const uint32_t staging_base = smem_base + ring_bytes;
   const uint32_t bias_off = ring_bytes + kStagingBytes;
-  const uint32_t bar_off = bias_off + 4u * BN * 4u;
+  const uint32_t bar_off = bias_off + kNumEpilogueWarps * BN * 4u;
   const uint32_t bar_base = smem_base + bar_off;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 2 + b); };
   auto res_bar = [&](int q, int b) { return bar_base + 8u * (2 * kMaxStages + 4 + q * kStagingDepth + b); };
-  constexpr uint32_t kNumBars = 2 * kMaxStages + 4 + 4 * kStagingDepth;
+  constexpr uint32_t kNumBars = 2 * kMaxStages + 4 + kNumEpilogueWarps * kStagingDepth;
   const uint32_t tmem_slot = bar_base + 8u * kNumBars;
   volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(smem_gen + bar_off + 8u * kNumBars);
   volatile uint32_t* abort_p = tmem_slot_p + 1;
@@ -338,7 +339,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), 4);   // one arrival per epilogue warp
     }
-    for (int q = 0; q < 4; ++q)
+    for (int q = 0; q < kNumEpilogueWarps; ++q)
       for (int b = 0; b < kStagingDepth; ++b) mbar_init(res_bar(q, b), 1);
     *abort_p = 0u;
     fence_mbar_init();
@@ -552,9 +553,13 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       TB200_PROF_STORE(4, clock64() - prof_t0);
     }
   } else {
-    // ------------------------------------------------------------ epilogue warps (2..5)
+    // ------------------------------------------------------------ epilogue warps (2..9)
+    // Two groups of four warps take alternate tiles of this CTA (group e drains TMEM accumulator e), so
+    // one tile's epilogue may take as long as two main loops before it holds the tensor pipe up.
     // Warp w may only read TMEM lanes [32*(w%4), 32*(w%4)+32): it owns those 32 output pixels of
     // the tile, one pixel per lane. Columns are processed in groups of 128 bytes of output.
+    const int ew = warp - 2;                       // 0..7
+    const int egroup = ew >> 2;                    // which accumulator / which tiles
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     OutT* __restrict__ out = static_cast<OutT*>(args.out);
@@ -564,15 +569,15 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     constexpr int kGroups = BN / kGroupCols;
     constexpr int kLdPerGroup = kGroupCols / 32;
     constexpr int kChunksPerLd = 32 / kVec;        // 16-byte chunks produced per 32-column TMEM load
-    float* bias_w = reinterpret_cast<float*>(smem_gen + bias_off) + quarter * BN;
-    const uint32_t bias_w_s = smem_base + bias_off + static_cast<uint32_t>(quarter * BN) * 4u;
-    const uint32_t stg0 = staging_base + static_cast<uint32_t>(quarter) * (kStagingDepth * kStagingBoxBytes);
+    float* bias_w = reinterpret_cast<float*>(smem_gen + bias_off) + ew * BN;
+    const uint32_t bias_w_s = smem_base + bias_off + static_cast<uint32_t>(ew * BN) * 4u;
+    const uint32_t stg0 = staging_base + static_cast<uint32_t>(ew) * (kStagingDepth * kStagingBoxBytes);
     const bool res_tma = args.res_tma != 0;
     // this lane's 16-byte chunk c of its staging row lives at row*128 + ((c ^ (row & 7)) << 4): the
     // SWIZZLE_128B pattern of the out / residual tensor maps (bank-conflict free for 8-lane phases)
     const uint32_t lane_row_off = static_cast<uint32_t>(lane) * 128u;
     const uint32_t lane_xor = static_cast<uint32_t>(lane) & 7u;
-    uint32_t box = 0;                              // staging box the next live group uses (0..2)
+    uint32_t box = 0;                              // staging box the next live group uses (0..1)
     uint32_t box_phase = 0;                        // bit b = parity of the next residual load into box b
     int bias_tile = -1;
     constexpr int kBiasPerLane = BN / 32;
@@ -589,19 +594,23 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         bias_next[j] = b;
       }
     };
-    if (static_cast<int>(blockIdx.x) < num_tiles) fetch_bias(static_cast<int>(blockIdx.x) % args.num_n_tiles);
-    int local_tile = 0;
+    // this group's tiles: blockIdx.x + (egroup + 2 i) * gridDim.x
+    const int etile0 = static_cast<int>(blockIdx.x) + egroup * static_cast<int>(gridDim.x);
+    const int estride = 2 * static_cast<int>(gridDim.x);
+    const int estep_m = estride / args.num_n_tiles, estep_n = estride % args.num_n_tiles;
+    if (etile0 < num_tiles) fetch_bias(etile0 % args.num_n_tiles);
+    int local_tile = egroup;
     bool ok = true;
     long long prof_wacc = 0, prof_wres = 0, prof_ld = 0, prof_math = 0, prof_stage = 0, prof_wstore = 0;
     (void)prof_wacc; (void)prof_wres; (void)prof_ld; (void)prof_math; (void)prof_stage; (void)prof_wstore;
     TB200_PROF_T(prof_t0);
-    int m_tile = first_m_tile - tile_step_m, n_tile = first_n_tile - tile_step_n;
+    int m_tile = etile0 / args.num_n_tiles - estep_m, n_tile = etile0 % args.num_n_tiles - estep_n;
     const bool need_coords = !args.out_tma || (res != nullptr && !res_tma);
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-      n_tile += tile_step_n; m_tile += tile_step_m;
+    for (int tile = etile0; tile < num_tiles && ok; tile += estride, local_tile += 2) {
+      n_tile += estep_n; m_tile += estep_m;
       if (n_tile >= args.num_n_tiles) { n_tile -= args.num_n_tiles; ++m_tile; }
       else if (n_tile < 0) { n_tile += args.num_n_tiles; --m_tile; }
-      const int buf = local_tile & 1;
+      const int buf = egroup;
       const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
       const int n_base = n_tile * BN;
       const int m_row0 = m_tile * kBlockM + quarter * 32;
@@ -615,8 +624,8 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         __syncwarp();
         bias_tile = n_tile;
       }
-      if (tile + static_cast<int>(gridDim.x) < num_tiles && tile_step_n != 0) {
-        int nn = n_tile + tile_step_n;
+      if (tile + estride < num_tiles && estep_n != 0) {
+        int nn = n_tile + estep_n;
         if (nn >= args.num_n_tiles) nn -= args.num_n_tiles;
         fetch_bias(nn);
       }
@@ -635,12 +644,12 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const OutT* res_row = res + res_off + static_cast<long long>(n_base) * args.res_sc;
 
       // Residual box of the tile's first live group: requested before the accumulator is waited for.
-      // Box `box` was last stored from three groups ago; at most the two newer stores may be pending.
+      // Box `box` was last stored from two groups ago; only the newer store may still be pending.
       if (res_tma && n_base < args.K_out) {
         if (lane == 0) {
-          bulk_wait_group_read<2>();
-          mbar_arrive_expect_tx(res_bar(quarter, box), kStagingBoxBytes);
-          tma_load_2d(stg0 + box * kStagingBoxBytes, &tmap_res, res_bar(quarter, box), n_base, m_row0);
+          bulk_wait_group_read<1>();
+          mbar_arrive_expect_tx(res_bar(ew, box), kStagingBoxBytes);
+          tma_load_2d(stg0 + box * kStagingBoxBytes, &tmap_res, res_bar(ew, box), n_base, m_row0);
         }
       }
 
@@ -661,16 +670,6 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int n0 = n_base + g * kGroupCols;
         const bool group_live = n0 < args.K_out;   // warp-uniform: false when the group is past K_out
         const uint32_t stg = stg0 + box * kStagingBoxBytes;
-        // residual box of the NEXT group goes into the next staging box, whose last store (three groups
-        // back) must have been read out; the store of the previous group may still be pending
-        if (res_tma && g + 1 < kGroups && n0 + kGroupCols < args.K_out) {
-          if (lane == 0) {
-            const uint32_t nb = (box + 1u) % kStagingDepth;
-            bulk_wait_group_read<1>();
-            mbar_arrive_expect_tx(res_bar(quarter, nb), kStagingBoxBytes);
-            tma_load_2d(stg0 + nb * kStagingBoxBytes, &tmap_res, res_bar(quarter, nb), n0 + kGroupCols, m_row0);
-          }
-        }
         uint32_t v[kLdPerGroup][32];
         TB200_PROF_T(tl);
 #pragma unroll
@@ -687,7 +686,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
         if (res_tma) {
           TB200_PROF_T(tw3);
-          const bool landed = mbar_wait_bounded(res_bar(quarter, box), (box_phase >> box) & 1u, abort_p,
+          const bool landed = mbar_wait_bounded(res_bar(ew, box), (box_phase >> box) & 1u, abort_p,
                                                 kWaitLimitCycles);
           TB200_PROF_ADD(prof_wres, tw3);
           if (!__all_sync(0xffffffffu, landed)) {
@@ -696,9 +695,19 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             break;
           }
           box_phase ^= (1u << box);
+          // Now that this group's residual has landed, fetch the NEXT group's into the other box. That
+          // box was stored from one group ago; its store has had this group's wait to be read out.
+          if (g + 1 < kGroups && n0 + kGroupCols < args.K_out) {
+            if (lane == 0) {
+              const uint32_t nb = box ^ 1u;
+              bulk_wait_group_read<0>();
+              mbar_arrive_expect_tx(res_bar(ew, nb), kStagingBoxBytes);
+              tma_load_2d(stg0 + nb * kStagingBoxBytes, &tmap_res, res_bar(ew, nb), n0 + kGroupCols, m_row0);
+            }
+          }
         } else if (args.out_tma) {
           TB200_PROF_T(ts);
-          if (lane == 0) bulk_wait_group_read<2>();   // this box's previous store has been read out
+          if (lane == 0) bulk_wait_group_read<1>();   // this box's previous store (two groups ago) has been read out
           __syncwarp();
           TB200_PROF_ADD(prof_wstore, ts);
         }
@@ -759,7 +768,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             tma_store_2d(&tmap_out, stg, n0, m_row0);
             bulk_commit_group();
           }
-          box = (box + 1u) % kStagingDepth;
+          box ^= 1u;
         }
         TB200_PROF_ADD(prof_stage, tg);
       }

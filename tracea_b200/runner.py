@@ -94,6 +94,23 @@ class ConvStack:
         if st != ffi.SUCCESS:
             raise ffi.TraceaError(st, "%s: %s" % (sp.name, ffi.last_error()))
 
+    def capture(self):
+        """Record one forward pass into a CUDA graph (launch-bound chains: 53 small launches cost more
+        host time than GPU time at small batch). Returns the graph; `replay()` runs it. The pass is run
+        once eagerly first so that every one-time set-up (kernel attributes, scratch pool growth) is
+        done before capture."""
+        self.forward()
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.forward()
+        self._graph = graph
+        return graph
+
+    def replay(self):
+        self._graph.replay()
+        return self.tensors[self.specs[-1].dst]
+
     @property
     def num_launches(self):
         return len(self._calls)
