@@ -179,6 +179,7 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     if rank == 0:
         build.build()
@@ -248,7 +249,7 @@ def run_ours(args):
     value = flops_step_rank * world * steps / (elapsed_max * 1e-3) / 1e12
 
     # ---- end to end through the C ABI with host tensors (H2D + D2H inside the timed region)
-    e2e_steps = max(2, min(steps, 8))
+    e2e_steps = max(3, min(steps, 15))
     host = {}
     g = torch.Generator().manual_seed(99 + rank)
     host["input"] = torch.randn((n, 1024, 14, 14), generator=g).abs_().to(torch.bfloat16).contiguous(
@@ -276,12 +277,19 @@ def run_ours(args):
 
     e2e_step()
     barrier()
-    t0 = time.perf_counter()
+    # every host-tensor call returns synchronised, so each step is timed on its own; the median is
+    # reported because the PCIe root and host memory are shared with other tenants of the machine
+    step_ms = []
     for _ in range(e2e_steps):
+        t0 = time.perf_counter()
         e2e_step()
+        torch.cuda.synchronize(dev)
+        step_ms.append((time.perf_counter() - t0) * 1e3)
     barrier()
-    e2e_ms = shard.max_over_ranks((time.perf_counter() - t0) * 1e3)
-    e2e_value = flops_step_rank * world * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    step_ms.sort()
+    e2e_median = shard.max_over_ranks(step_ms[len(step_ms) // 2])
+    e2e_mean = shard.max_over_ranks(sum(step_ms) / len(step_ms))
+    e2e_value = flops_step_rank * world / (e2e_median * 1e-3) / 1e12
 
     # ---- the whole ResNet-50 conv stack (53 fused convs), images/s, as an extra figure
     extra = {}
@@ -356,7 +364,8 @@ def run_ours(args):
                          "traffic": CONV3X3_NCU_TRAFFIC_BYTES, "algorithmic_bytes": resnet50.conv_bytes(c2, n),
                          "hbm_peak_gbs": peaks["hbm_gbs"]},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world,
-                    "d2h_bytes_per_step": d2h * world, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+                    "d2h_bytes_per_step": d2h * world, "steps": e2e_steps, "ms_per_step": e2e_median,
+                    "ms_per_step_mean": e2e_mean, "stat": "median of the per-step times"},
             "gpu_launches": steps * nl * world,
             "clocks": clocks.summary(),
             "resnet50": extra,

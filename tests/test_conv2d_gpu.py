@@ -386,6 +386,26 @@ def test_host_memory_tensors_are_staged_through_the_gpu():
     assert cc.rel_err(out, want) <= cc.TOL_TF32
 
 
+def test_large_host_batches_are_pipelined_in_chunks_with_identical_results(monkeypatch):
+    """Host tensors above a few MB are cut into image chunks whose copy-in, kernels and copy-out overlap;
+    the result must be bit-identical to the single-shot staging and match the oracle."""
+    n = 36
+    x = cc.uniform((n, 64, 32, 32), 5, "hostc/x")
+    w = cc.kaiming((64, 64, 3, 3), 5, "hostc/w")
+    b = cc.normal((64,), 5, "hostc/b", 0.1)
+    r = cc.normal((n, 64, 32, 32), 5, "hostc/r")
+    mk = lambda a: ffi.View(a.ctypes.data, a.shape, [s // 4 for s in a.strides], ffi.DTYPE_FLOAT32, -1)
+    outs = []
+    for chunks in ("1", "8", "5"):
+        monkeypatch.setenv("TRACEA_B200_HOST_CHUNKS", chunks)
+        out = np.full((n, 64, 32, 32), np.nan, np.float32)
+        ffi.conv2d_raw(mk(x), mk(w), mk(b), mk(r), mk(out), padding=(1, 1), epilogue=ffi.EPILOGUE_BIAS_RESIDUAL_RELU)
+        outs.append(out)
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    want = oracle.conv2d_gemm(cc.channels_last(x), w, b, r, 1, 1, 1, "relu")
+    assert cc.rel_err(outs[1], want) <= cc.TOL_TF32
+
+
 def test_work_is_enqueued_on_the_callers_stream():
     x = to_dev(cc.uniform((4, 64, 14, 14), 6, "st/x"), "bf16")
     w = to_dev(cc.kaiming((64, 64, 3, 3), 6, "st/w"), "bf16")

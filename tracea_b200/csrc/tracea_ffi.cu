@@ -74,10 +74,16 @@ struct DeviceState {
   cudaMemPool_t pool = nullptr;
   uint32_t* status = nullptr;  // pinned, mapped: kernels write error codes the host reads directly
   bool attr_set[3][3] = {};    // [dtype][bn index]
+  // host-memory path only: copy streams and events for the chunked H2D / compute / D2H pipeline
+  static constexpr int kMaxChunks = 16;
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t ev_entry = nullptr, ev_done = nullptr;
+  cudaEvent_t ev_in[kMaxChunks] = {}, ev_out[kMaxChunks] = {};
 };
 
 constexpr int kMaxDevices = 64;
 std::mutex g_mutex;
+std::mutex g_host_path_mutex;   // one host-memory call at a time per process (it owns the copy streams)
 DeviceState g_dev[kMaxDevices];
 EncodeTiledFn g_encode_tiled = nullptr;
 EncodeIm2colFn g_encode_im2col = nullptr;
@@ -858,25 +864,92 @@ void conv2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, cons
   }
 
   // Host memory: stage through the current CUDA device, run the same device path, copy back and
-  // wait, so that the result is in the caller's buffer when the call returns.
+  // wait, so that the result is in the caller's buffer when the call returns. Large batches are cut
+  // into chunks of images so that the copy in of chunk i+1, the kernels of chunk i and the copy out
+  // of chunk i-1 overlap (PCIe is full duplex; the kernels are a small fraction of the copy time).
   int cur = 0;
   TB_CUDA(cudaGetDevice(&cur));
   cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
+  std::lock_guard<std::mutex> host_lock(g_host_path_mutex);
+  const bool use_bias = bias != nullptr && epi.bias, use_res = res != nullptr && epi.residual;
+  auto image_major = [](const View4& v) {   // images do not interleave: one image's span fits in stride[0]
+    long long span = 1;
+    for (int i = 1; i < 4; ++i) span += (v.shape[i] - 1) * v.stride[i];
+    return v.shape[0] == 1 || v.stride[0] >= span;
+  };
+  auto image_span = [](const View4& v) {
+    long long span = 1;
+    for (int i = 1; i < 4; ++i) span += (v.shape[i] - 1) * v.stride[i];
+    return span;
+  };
+  const long long total_bytes = (span_elems(x) + span_elems(out) + (use_res ? span_elems(*res) : 0)) * es;
+  int chunks = 1;
+  if (N >= 16 && total_bytes >= (8LL << 20) && image_major(x) && image_major(out) && span_elems(out) == num_elems(out) &&
+      (!use_res || image_major(*res)) && env_int("TRACEA_B200_HOST_CHUNKS", 8) > 1) {
+    chunks = std::min<long long>({(long long)env_int("TRACEA_B200_HOST_CHUNKS", 8), (long long)DeviceState::kMaxChunks, N / 2});
+  }
   Staged sx, sw, sb, sr, so;
+  DeviceState* stp = nullptr;
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     DeviceState& st = device_state(cur);
-    stage_in(st, x, sx, stream, true);
+    stp = &st;
+    stage_in(st, x, sx, stream, chunks == 1);
     stage_in(st, w, sw, stream, true);
-    if (bias != nullptr && epi.bias) stage_in(st, *bias, sb, stream, true);
-    if (res != nullptr && epi.residual) stage_in(st, *res, sr, stream, true);
+    if (use_bias) stage_in(st, *bias, sb, stream, true);
+    if (use_res) stage_in(st, *res, sr, stream, chunks == 1);
     // a strided `out` has gaps the copy back must not clobber: seed the staging buffer with them
     stage_in(st, out, so, stream, span_elems(out) != num_elems(out));
+    if (chunks > 1 && st.copy_in == nullptr) {
+      TB_CUDA(cudaStreamCreateWithFlags(&st.copy_in, cudaStreamNonBlocking));
+      TB_CUDA(cudaStreamCreateWithFlags(&st.copy_out, cudaStreamNonBlocking));
+      TB_CUDA(cudaEventCreateWithFlags(&st.ev_entry, cudaEventDisableTiming));
+      TB_CUDA(cudaEventCreateWithFlags(&st.ev_done, cudaEventDisableTiming));
+      for (int i = 0; i < DeviceState::kMaxChunks; ++i) {
+        TB_CUDA(cudaEventCreateWithFlags(&st.ev_in[i], cudaEventDisableTiming));
+        TB_CUDA(cudaEventCreateWithFlags(&st.ev_out[i], cudaEventDisableTiming));
+      }
+    }
   }
-  conv2d_device(cur, sx.view, sw.view, (bias != nullptr && epi.bias) ? &sb.view : nullptr,
-                (res != nullptr && epi.residual) ? &sr.view : nullptr, so.view, p, epi);
-  TB_CUDA(cudaMemcpyAsync(out.ptr, so.buf.ptr, static_cast<size_t>(span_elems(out)) * es,
-                          cudaMemcpyDeviceToHost, stream));
+  if (chunks == 1) {
+    conv2d_device(cur, sx.view, sw.view, use_bias ? &sb.view : nullptr, use_res ? &sr.view : nullptr, so.view, p, epi);
+    TB_CUDA(cudaMemcpyAsync(out.ptr, so.buf.ptr, static_cast<size_t>(span_elems(out)) * es,
+                            cudaMemcpyDeviceToHost, stream));
+  } else {
+    DeviceState& st = *stp;
+    // the staging buffers were allocated in stream order on `stream`: the copy streams start after that point
+    TB_CUDA(cudaEventRecord(st.ev_entry, stream));
+    TB_CUDA(cudaStreamWaitEvent(st.copy_in, st.ev_entry, 0));
+    TB_CUDA(cudaStreamWaitEvent(st.copy_out, st.ev_entry, 0));
+    auto chunk_of = [&](const View4& dev_view, long long n0, long long n1) {
+      View4 c = dev_view;
+      c.ptr = static_cast<char*>(dev_view.ptr) + n0 * dev_view.stride[0] * es;
+      c.shape[0] = n1 - n0;
+      return c;
+    };
+    auto copy_chunk = [&](void* dst_base, const void* src_base, const View4& v, long long n0, long long n1,
+                          cudaMemcpyKind kind, cudaStream_t s) {
+      const size_t off = static_cast<size_t>(n0 * v.stride[0]) * es;
+      const size_t len = static_cast<size_t>((n1 - n0 - 1) * v.stride[0] + image_span(v)) * es;
+      TB_CUDA(cudaMemcpyAsync(static_cast<char*>(dst_base) + off, static_cast<const char*>(src_base) + off, len, kind, s));
+    };
+    for (int c = 0; c < chunks; ++c) {
+      const long long n0 = N * c / chunks, n1 = N * (c + 1) / chunks;
+      copy_chunk(sx.buf.ptr, x.ptr, x, n0, n1, cudaMemcpyHostToDevice, st.copy_in);
+      if (use_res) copy_chunk(sr.buf.ptr, res->ptr, *res, n0, n1, cudaMemcpyHostToDevice, st.copy_in);
+      TB_CUDA(cudaEventRecord(st.ev_in[c], st.copy_in));
+      TB_CUDA(cudaStreamWaitEvent(stream, st.ev_in[c], 0));
+      const View4 xc = chunk_of(sx.view, n0, n1), oc = chunk_of(so.view, n0, n1);
+      View4 rc;
+      if (use_res) rc = chunk_of(sr.view, n0, n1);
+      conv2d_device(cur, xc, sw.view, use_bias ? &sb.view : nullptr, use_res ? &rc : nullptr, oc, p, epi);
+      TB_CUDA(cudaEventRecord(st.ev_out[c], stream));
+      TB_CUDA(cudaStreamWaitEvent(st.copy_out, st.ev_out[c], 0));
+      copy_chunk(out.ptr, so.buf.ptr, out, n0, n1, cudaMemcpyDeviceToHost, st.copy_out);
+    }
+    TB_CUDA(cudaEventRecord(st.ev_done, st.copy_out));
+    TB_CUDA(cudaStreamWaitEvent(stream, st.ev_done, 0));
+  }
   TB_CUDA(cudaStreamSynchronize(stream));
   const uint32_t code = tracea_b200_device_status(cur);
   if (code != 0u) TB_FAIL(TRACEA_CUDA_ERROR, "conv kernel gave up a bounded wait (code %u)", code);
@@ -967,6 +1040,16 @@ void tracea_shutdown(void) {
     cudaGetDevice(&prev);
     cudaSetDevice(d);
     cudaDeviceSynchronize();
+    if (st.copy_in != nullptr) {
+      cudaStreamDestroy(st.copy_in);
+      cudaStreamDestroy(st.copy_out);
+      cudaEventDestroy(st.ev_entry);
+      cudaEventDestroy(st.ev_done);
+      for (int i = 0; i < DeviceState::kMaxChunks; ++i) {
+        cudaEventDestroy(st.ev_in[i]);
+        cudaEventDestroy(st.ev_out[i]);
+      }
+    }
     if (st.pool != nullptr) cudaMemPoolDestroy(st.pool);
     if (st.status != nullptr) cudaFreeHost(st.status);
     st = DeviceState();
