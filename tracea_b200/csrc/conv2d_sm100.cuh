@@ -60,6 +60,7 @@ struct ConvKernelArgs {
   int total_chunks;       // R * S * chunks_per_tap
   int C;                  // input channels (c coordinate >= C reads zeros)
   int a_tiled;            // 1: A is a plain [M][C] matrix (1x1, stride 1, no padding) read by tiled TMA
+  int prefetch_dist;      // > 0: the producer L2-prefetches A this many k-steps ahead of its loads
   // tiling / pipeline
   int num_m_tiles, num_n_tiles;
   int num_stages;
@@ -387,6 +388,42 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       (void)prof_wait;
       TB200_PROF_T(prof_t0);
       bool slot_free = mbar_test_wait(empty_addr, phase ^ 1u);
+      // L2 prefetch cursor: walks the same (tile, k-step) sequence as the loads, `prefetch_dist` steps ahead
+      struct {
+        int tile, m_tile, n_tile, it, w_start, h_start, img0, c_coord, tap_s;
+        uint32_t off_w, off_h;
+      } pf = {};
+      auto pf_begin_tile = [&]() {
+        const int pm0 = pf.m_tile * kBlockM;
+        const int pt = pm0 / args.Wo;
+        pf.w_start = (pm0 % args.Wo) * args.stride_w - args.pad_w;
+        pf.h_start = (pt % args.Ho) * args.stride_h - args.pad_h;
+        pf.img0 = pt / args.Ho;
+        pf.it = 0; pf.c_coord = 0; pf.tap_s = 0; pf.off_w = 0; pf.off_h = 0;
+      };
+      auto pf_step = [&]() {   // issue one prefetch (if any work is left) and advance
+        if (pf.tile >= num_tiles) return;
+        tma_prefetch_im2col_4d(&tmap_x, pf.c_coord, pf.w_start, pf.h_start, pf.img0, (uint16_t)pf.off_w,
+                               (uint16_t)pf.off_h);
+        pf.c_coord += args.chunk_elems;
+        if (pf.c_coord == args.C) {
+          pf.c_coord = 0;
+          pf.off_w += args.dil_w;
+          if (++pf.tap_s == args.S) { pf.tap_s = 0; pf.off_w = 0; pf.off_h += args.dil_h; }
+        }
+        if (++pf.it == k_iters) {
+          pf.tile += gridDim.x;
+          pf.n_tile += tile_step_n; pf.m_tile += tile_step_m;
+          if (pf.n_tile >= args.num_n_tiles) { pf.n_tile -= args.num_n_tiles; ++pf.m_tile; }
+          if (pf.tile < num_tiles) pf_begin_tile();
+        }
+      };
+      const bool do_prefetch = one_chunk && args.prefetch_dist > 0;
+      if (do_prefetch) {
+        pf.tile = blockIdx.x; pf.m_tile = first_m_tile; pf.n_tile = first_n_tile;
+        if (pf.tile < num_tiles) pf_begin_tile();
+        for (int i = 0; i < args.prefetch_dist; ++i) pf_step();
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = m_tile * kBlockM;
         const int q0 = m0 % args.Wo;
@@ -415,6 +452,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 tma_stage_probe(stage_addr, stage_addr + kABytes, full_addr, kStageBytes, &tmap_x, c_coord, w_start,
                                 h_start, img0, (uint16_t)off_w, (uint16_t)off_h, &tmap_w, k_coord, n_coord, nempty,
                                 nphase ^ 1u);
+            if (do_prefetch) pf_step();
             k_coord += args.chunk_elems;
             c_coord += args.chunk_elems;
             if (c_coord == args.C) {

@@ -15,18 +15,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred = 0;
-  asm volatile(
-      "{\n"
-      ".reg .pred P;\n"
-      "elect.sync _|P, 0xffffffff;\n"
-      "selp.u32 %0, 1, 0, P;\n"
-      "}\n"
-      : "=r"(pred));
-  return pred != 0;
-}
-
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -122,6 +110,16 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* tma
       : "memory");
 }
 
+// Same im2col box, but only pulled into L2 (no shared-memory destination, no barrier): used to run the
+// HBM fetch of the activations several k-steps ahead of the shared-memory ring.
+__device__ __forceinline__ void tma_prefetch_im2col_4d(const void* tmap, int c, int w, int h, int n, uint16_t off_w,
+                                                       uint16_t off_h) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.im2col [%0, {%1, %2, %3, %4}], {%5, %6};"
+               :
+               : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+               : "memory");
+}
+
 // Tiled 2-D store shared -> global (bulk-group completion). Rows / columns outside the tensor are
 // clipped by the TMA unit, which is what handles the M and K_out tails.
 __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int c0, int c1) {
@@ -132,10 +130,6 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int
 }
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-// All bulk groups of this thread have finished READING shared memory (the source may be reused).
-__device__ __forceinline__ void bulk_wait_group_read0() {
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 // At most N of this thread's most recent bulk groups may still be reading shared memory.
 template <int N>
@@ -184,66 +178,6 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// D[tmem] (+)= A[smem] * B[smem], 16-bit inputs (f16 / bf16), fp32 accumulate.
-__device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                           uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n"
-      :
-      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Same with fp32 inputs consumed as TF32.
-__device__ __forceinline__ void mma_tf32_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
-      "}\n"
-      :
-      : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Lean issue forms for the hot loop: descriptors arrive as (lo, hi) register pairs and the
-// accumulate predicate is a compile-time constant, so one MMA costs two integer adds plus the
-// instruction itself in the issuing thread. kTf32 selects kind::tf32 instead of kind::f16.
-template <bool kTf32, bool kAccumulate>
-__device__ __forceinline__ void mma_ss_lean(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
-                                            uint32_t idesc) {
-  if constexpr (kTf32) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        ".reg .b64 da, db;\n"
-        "setp.ne.b32 p, %5, 0;\n"
-        "mov.b64 da, {%1, %3};\n"
-        "mov.b64 db, {%2, %3};\n"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n"
-        "}\n"
-        :
-        : "r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        ".reg .b64 da, db;\n"
-        "setp.ne.b32 p, %5, 0;\n"
-        "mov.b64 da, {%1, %3};\n"
-        "mov.b64 db, {%2, %3};\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
-        "}\n"
-        :
-        : "r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
-        : "memory");
-  }
-}
 // One pipeline stage of the MMA issuer as a single block: probe the NEXT stage's full barrier, issue
 // the four MMAs of this stage, commit them to this stage's empty barrier, and only then read the
 // probe's predicate -- so the probe's latency is spent under the MMA issue instead of stalling the
@@ -344,22 +278,12 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 
 // ------------------------------------------------------------------ descriptors
-// Shared-memory matrix descriptor (64-bit) for tcgen05.mma operands.
+// Shared-memory matrix descriptor (64-bit) for tcgen05.mma operands; the kernel assembles it from a
+// precomputed low word (address + leading-dimension offset) and a constant high word.
 //   [0,14)  start address >> 4      [16,30) leading-dim byte offset >> 4
 //   [32,46) stride-dim byte offset >> 4   [46,48) descriptor version (1 on sm_100)
 //   [49,52) base offset (0: stage buffers are 1024-B aligned)   [61,64) swizzle mode
 // Swizzle modes: 0 none, 2 = 128 B, 4 = 64 B, 6 = 32 B.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes, uint32_t swizzle_mode) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(swizzle_mode & 7u) << 61;
-  return d;
-}
-
 // Instruction descriptor (32-bit) for kind::f16 / kind::tf32, dense, fp32 accumulate,
 // both operands K-major.
 //   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format

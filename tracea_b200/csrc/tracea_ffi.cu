@@ -656,6 +656,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   a.total_chunks = static_cast<int>(total_chunks_ll);
   a.C = static_cast<int>(Cg);
   a.a_tiled = a_tiled ? 1 : 0;
+  a.prefetch_dist = env_int("TRACEA_B200_PREFETCH", 0);
   a.num_m_tiles = static_cast<int>(m_tiles);
   a.num_n_tiles = static_cast<int>(n_tiles);
   a.num_stages = stages;
