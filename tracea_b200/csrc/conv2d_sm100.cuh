@@ -156,8 +156,10 @@ constexpr int kStagingBoxBytes = 32 * 128;
 constexpr int kStagingDepth = 2;
 constexpr int kNumEpilogueWarps = 8;
 constexpr int kStagingBytes = kNumEpilogueWarps * kStagingDepth * kStagingBoxBytes;
-__host__ __device__ constexpr int conv_smem_bytes(int bn, int stages) {
-  return stages * (kBlockM * kStageKBytes + bn * kStageKBytes) + kStagingBytes + kNumEpilogueWarps * bn * 4 + 512 + 1024;
+// `pair`: two CTAs on neighbouring SMs work on one 256-row tile and each holds only half of B's rows.
+__host__ __device__ constexpr int conv_smem_bytes(int bn, int stages, bool pair = false) {
+  return stages * (kBlockM * kStageKBytes + (pair ? bn / 2 : bn) * kStageKBytes) + kStagingBytes +
+         kNumEpilogueWarps * bn * 4 + 512 + 1024;
 }
 
 // 8 consecutive fp32 values -> one 16-byte vector of OutT (16-bit types) / 4 values (fp32).
@@ -295,7 +297,10 @@ __device__ __noinline__ void epilogue_block_generic(const ConvKernelArgs& args, 
   }
 }
 
-template <typename OutT, int BN>
+// kPair: launched as clusters of two CTAs (cta_group::2). The pair owns a 256 x BN tile: each CTA loads its own
+// 128 pixels of A and its own half of B's rows (no multicast), the leader CTA issues M = 256 MMAs that span both
+// SMs, each CTA drains its own 128 TMEM lanes. Per CTA this halves the B bytes brought in per MMA.
+template <typename OutT, int BN, bool kPair>
 __global__ void __launch_bounds__(kNumThreads, 1)
 conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ CUtensorMap tmap_w,
@@ -304,8 +309,15 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ ConvKernelArgs args) {
   using namespace ptx;
   constexpr uint32_t kABytes = kBlockM * kStageKBytes;   // 16 KB
-  constexpr uint32_t kBBytes = BN * kStageKBytes;
+  constexpr uint32_t kBRows = kPair ? BN / 2 : BN;       // rows of B this CTA keeps in shared memory
+  constexpr uint32_t kBBytes = kBRows * kStageKBytes;
   constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  constexpr int kTileM = kPair ? 2 * kBlockM : kBlockM;  // output pixels per tile (of the pair)
+  const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0u;
+  // tiles are dealt to CTAs (or CTA pairs) round robin
+  const int worker = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int num_workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   constexpr uint32_t kTmemCols = 2 * BN;                 // two accumulators: 128, 256 or 512 columns
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
 
@@ -338,7 +350,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);   // one arrival per epilogue warp
+      mbar_init(tempty_bar(b), kPair ? 8 : 4);   // one arrival per epilogue warp (of both CTAs of a pair)
     }
     for (int q = 0; q < kNumEpilogueWarps; ++q)
       for (int b = 0; b < kStagingDepth; ++b) mbar_init(res_bar(q, b), 1);
@@ -350,11 +362,17 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (args.res_tma) prefetch_tmap(&tmap_res);
   }
   if (warp == 1) {
-    tmem_alloc<kTmemCols>(tmem_slot);
-    tmem_relinquish();
+    if constexpr (kPair) {
+      tmem_alloc_pair<kTmemCols>(tmem_slot);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc<kTmemCols>(tmem_slot);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (kPair) cluster_sync();   // the peer's barriers are initialised before anything signals them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_p;
 
@@ -362,12 +380,13 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int chunks_per_stage = kStageKBytes / args.chunk_bytes;
   const int k_iters = (args.total_chunks + chunks_per_stage - 1) / chunks_per_stage;
 
-  // Tiles are walked as (m_tile, n_tile) pairs advanced without divisions: tile += gridDim.x.
-  const int tile_step_m = static_cast<int>(gridDim.x) / args.num_n_tiles;
-  const int tile_step_n = static_cast<int>(gridDim.x) % args.num_n_tiles;
-  const int first_m_tile = static_cast<int>(blockIdx.x) / args.num_n_tiles;
-  const int first_n_tile = static_cast<int>(blockIdx.x) % args.num_n_tiles;
+  // Tiles are walked as (m_tile, n_tile) pairs advanced without divisions: tile += num_workers.
+  const int tile_step_m = num_workers / args.num_n_tiles;
+  const int tile_step_n = num_workers % args.num_n_tiles;
+  const int first_m_tile = worker / args.num_n_tiles;
+  const int first_n_tile = worker % args.num_n_tiles;
   const uint32_t full_bar0 = bar_base, empty_bar0 = bar_base + 8u * kMaxStages;
+  const uint32_t full_leader0 = kPair ? mapa_cluster(full_bar0, 0u) : full_bar0;   // leader's full barriers
   const uint32_t ring_end = smem_base + ring_bytes;
 
   if (warp == 0) {
@@ -394,7 +413,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         uint32_t off_w, off_h;
       } pf = {};
       auto pf_begin_tile = [&]() {
-        const int pm0 = pf.m_tile * kBlockM;
+        const int pm0 = pf.m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
         const int pt = pm0 / args.Wo;
         pf.w_start = (pm0 % args.Wo) * args.stride_w - args.pad_w;
         pf.h_start = (pt % args.Ho) * args.stride_h - args.pad_h;
@@ -412,7 +431,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (++pf.tap_s == args.S) { pf.tap_s = 0; pf.off_w = 0; pf.off_h += args.dil_h; }
         }
         if (++pf.it == k_iters) {
-          pf.tile += gridDim.x;
+          pf.tile += num_workers;
           pf.n_tile += tile_step_n; pf.m_tile += tile_step_m;
           if (pf.n_tile >= args.num_n_tiles) { pf.n_tile -= args.num_n_tiles; ++pf.m_tile; }
           if (pf.tile < num_tiles) pf_begin_tile();
@@ -420,19 +439,19 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       };
       const bool do_prefetch = one_chunk && args.prefetch_dist > 0;
       if (do_prefetch) {
-        pf.tile = blockIdx.x; pf.m_tile = first_m_tile; pf.n_tile = first_n_tile;
+        pf.tile = worker; pf.m_tile = first_m_tile; pf.n_tile = first_n_tile;
         if (pf.tile < num_tiles) pf_begin_tile();
         for (int i = 0; i < args.prefetch_dist; ++i) pf_step();
       }
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = m_tile * kBlockM;
+      for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
+        const int m0 = m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;   // this CTA's 128 pixels
         const int q0 = m0 % args.Wo;
         const int t = m0 / args.Wo;
         const int p0 = t % args.Ho;
         const int img0 = t / args.Ho;
         const int w_start = q0 * args.stride_w - args.pad_w;
         const int h_start = p0 * args.stride_h - args.pad_h;
-        const int n_coord = n_tile * BN;
+        const int n_coord = n_tile * BN + static_cast<int>(cta_rank * kBRows);   // this CTA's rows of B
         if (one_chunk) {
           // common case: one 128-byte chunk per stage = 64 (16-bit) or 32 (fp32) channels of one tap
           int c_coord = 0, k_coord = 0, tap_s = 0;
@@ -448,10 +467,18 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             // probe the next slot now; the answer is read at the top of the next iteration
             uint32_t nstage = stage_addr + kStageBytes, nfull = full_addr + 8u, nempty = empty_addr + 8u, nphase = phase;
             if (nstage == ring_end) { nstage = smem_base; nfull = full_bar0; nempty = empty_bar0; nphase ^= 1u; }
-            const bool next_free =
-                tma_stage_probe(stage_addr, stage_addr + kABytes, full_addr, kStageBytes, &tmap_x, c_coord, w_start,
-                                h_start, img0, (uint16_t)off_w, (uint16_t)off_h, &tmap_w, k_coord, n_coord, nempty,
-                                nphase ^ 1u);
+            bool next_free;
+            if constexpr (kPair) {
+              // both CTAs' copies complete on the leader's full barrier; the leader arms it for both
+              next_free = tma_stage_probe_pair(stage_addr, stage_addr + kABytes, full_addr,
+                                               full_leader0 + (full_addr - full_bar0), leader ? 2u * kStageBytes : 0u,
+                                               &tmap_x, c_coord, w_start, h_start, img0, (uint16_t)off_w,
+                                               (uint16_t)off_h, &tmap_w, k_coord, n_coord, nempty, nphase ^ 1u);
+            } else {
+              next_free = tma_stage_probe(stage_addr, stage_addr + kABytes, full_addr, kStageBytes, &tmap_x, c_coord,
+                                          w_start, h_start, img0, (uint16_t)off_w, (uint16_t)off_h, &tmap_w, k_coord,
+                                          n_coord, nempty, nphase ^ 1u);
+            }
             if (do_prefetch) pf_step();
             k_coord += args.chunk_elems;
             c_coord += args.chunk_elems;
@@ -527,7 +554,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // One thread. Descriptor low words are precomputed per k-slice; per stage they only move by the
     // stage pitch, so an MMA costs two adds and one instruction here (the tensor pipe needs a new
     // 128 x BN x 32-byte MMA every BN/2 cycles).
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       constexpr bool kTf32 = OutTraits<OutT>::kTf32;
       const uint32_t desc_hi = ((args.a_sbo >> 4) & 0x3FFFu) | (1u << 14) | ((args.swizzle_mode & 7u) << 29);
       uint32_t a_k[4], b_k[4];
@@ -548,7 +575,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       (void)prof_wfull; (void)prof_wtmem;
       TB200_PROF_T(prof_t0);
       bool stage_ready = mbar_test_wait(full_addr, phase);
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      for (int tile = worker; tile < num_tiles && ok; tile += num_workers, ++local_tile) {
         const int buf = local_tile & 1;
         const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
         TB200_PROF_T(tw0);
@@ -573,18 +600,34 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (n_off == ring_units) { n_off = 0; nfull = full_bar0; nempty = empty_bar0; nphase ^= 1u; }
           tc_fence_after();
           bool next_ready;
-          if (it == 0)
-            next_ready = mma_stage4_probe<kTf32, false>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
-                                                        a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off,
-                                                        b_k[3] + s_off, desc_hi, idesc, empty_addr, nfull, nphase);
-          else
-            next_ready = mma_stage4_probe<kTf32, true>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
-                                                       a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off,
-                                                       b_k[3] + s_off, desc_hi, idesc, empty_addr, nfull, nphase);
+          if constexpr (kPair) {
+            if (it == 0)
+              next_ready = mma_stage4_probe_pair<kTf32, false>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
+                                                               a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off,
+                                                               b_k[2] + s_off, b_k[3] + s_off, desc_hi, idesc,
+                                                               empty_addr, nfull, nphase);
+            else
+              next_ready = mma_stage4_probe_pair<kTf32, true>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
+                                                              a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off,
+                                                              b_k[2] + s_off, b_k[3] + s_off, desc_hi, idesc,
+                                                              empty_addr, nfull, nphase);
+          } else {
+            if (it == 0)
+              next_ready = mma_stage4_probe<kTf32, false>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
+                                                          a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off,
+                                                          b_k[3] + s_off, desc_hi, idesc, empty_addr, nfull, nphase);
+            else
+              next_ready = mma_stage4_probe<kTf32, true>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
+                                                         a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off,
+                                                         b_k[3] + s_off, desc_hi, idesc, empty_addr, nfull, nphase);
+          }
           s_off = n_off; full_addr = nfull; empty_addr = nempty; phase = nphase;
           stage_ready = next_ready;
         }
-        if (ok) mma_commit(tfull_bar(buf));       // accumulator complete
+        if (ok) {                                 // accumulator complete (in both CTAs of a pair)
+          if constexpr (kPair) mma_commit_pair(tfull_bar(buf));
+          else mma_commit(tfull_bar(buf));
+        }
       }
       TB200_PROF_STORE(2, prof_wfull);
       TB200_PROF_STORE(3, prof_wtmem);
@@ -632,9 +675,9 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         bias_next[j] = b;
       }
     };
-    // this group's tiles: blockIdx.x + (egroup + 2 i) * gridDim.x
-    const int etile0 = static_cast<int>(blockIdx.x) + egroup * static_cast<int>(gridDim.x);
-    const int estride = 2 * static_cast<int>(gridDim.x);
+    // this group's tiles: worker + (egroup + 2 i) * num_workers
+    const int etile0 = worker + egroup * num_workers;
+    const int estride = 2 * num_workers;
     const int estep_m = estride / args.num_n_tiles, estep_n = estride % args.num_n_tiles;
     if (etile0 < num_tiles) fetch_bias(etile0 % args.num_n_tiles);
     int local_tile = egroup;
@@ -651,7 +694,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int buf = egroup;
       const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
       const int n_base = n_tile * BN;
-      const int m_row0 = m_tile * kBlockM + quarter * 32;
+      const int m_row0 = m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM + quarter * 32;
 
       // this warp's fp32 copy of the tile's bias (zeros when there is none / past K_out); the values
       // were fetched into registers during the previous tile, and the next tile's are fetched now
@@ -668,7 +711,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         fetch_bias(nn);
       }
 
-      const int m = m_tile * kBlockM + row;
+      const int m = m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM + row;
       const bool row_ok = m < args.M;
       long long out_off = 0, res_off = 0;
       if (need_coords) {   // only the per-lane store / load paths need (n, ho, wo); the TMA paths do not
@@ -718,7 +761,10 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           // the accumulator is in registers now: hand the TMEM buffer back to the MMA issuer
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(buf));
+          if (lane == 0) {
+            if constexpr (kPair) mbar_arrive_cluster(mapa_cluster(tempty_bar(buf), 0u));   // the leader's barrier
+            else mbar_arrive(tempty_bar(buf));
+          }
         }
         if (!group_live) continue;
 
@@ -825,10 +871,12 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
-  __syncthreads();
+  if constexpr (kPair) cluster_sync();   // neither CTA frees TMEM or exits while the other may still use the pair
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc<kTmemCols>(tmem_base);
+    if constexpr (kPair) tmem_dealloc_pair<kTmemCols>(tmem_base);
+    else tmem_dealloc<kTmemCols>(tmem_base);
   }
 }
 

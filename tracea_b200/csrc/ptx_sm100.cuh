@@ -15,6 +15,27 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ------------------------------------------------------------------ CTA pairs (cluster of 2)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Barrier over every thread of both CTAs of the cluster (all threads must call it).
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_cluster(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -171,6 +192,19 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(kCols)
                : "memory");
 }
+// cta_group::2 forms: the TMEM columns are allocated in both CTAs of the pair; each CTA's MMA warp calls these.
+template <uint32_t kCols>
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(kCols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <uint32_t kCols>
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(kCols) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -223,6 +257,94 @@ __device__ __forceinline__ bool mma_stage4_probe(uint32_t tmem_d, uint32_t a0, u
   }
 #undef TB200_MMA_STAGE
   return ready != 0;
+}
+
+// The same stage for a CTA pair: issued by the leader CTA only; each MMA spans both SMs (M = 256: 128 rows of
+// A and half of B's rows come from each CTA's shared memory at the same offsets) and the commit arrives on
+// the `empty` barrier at the same offset in BOTH CTAs (multicast arrive, mask 0b11).
+template <bool kTf32, bool kFirstAccumulates>
+__device__ __forceinline__ bool mma_stage4_probe_pair(uint32_t tmem_d, uint32_t a0, uint32_t a1, uint32_t a2,
+                                                      uint32_t a3, uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3,
+                                                      uint32_t desc_hi, uint32_t idesc, uint32_t empty_bar,
+                                                      uint32_t next_full_bar, uint32_t next_parity) {
+  uint32_t ready;
+#define TB200_MMA_STAGE2(KIND)                                                                  \
+  asm volatile(                                                                                  \
+      "{\n"                                                                                      \
+      ".reg .pred pn, p0, p1;\n"                                                                 \
+      ".reg .b64 da, db;\n"                                                                      \
+      ".reg .b16 msk;\n"                                                                         \
+      "mov.b16 msk, 3;\n"                                                                        \
+      "mbarrier.test_wait.parity.shared::cta.b64 pn, [%13], %14;\n"                              \
+      "setp.ne.b32 p0, %15, 0;\n"                                                                \
+      "setp.eq.b32 p1, 0, 0;\n"                                                                  \
+      "mov.b64 da, {%2, %10};\n"                                                                 \
+      "mov.b64 db, {%6, %10};\n"                                                                 \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%1], da, db, %11, p0;\n"                         \
+      "mov.b64 da, {%3, %10};\n"                                                                 \
+      "mov.b64 db, {%7, %10};\n"                                                                 \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%1], da, db, %11, p1;\n"                         \
+      "mov.b64 da, {%4, %10};\n"                                                                 \
+      "mov.b64 db, {%8, %10};\n"                                                                 \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%1], da, db, %11, p1;\n"                         \
+      "mov.b64 da, {%5, %10};\n"                                                                 \
+      "mov.b64 db, {%9, %10};\n"                                                                 \
+      "tcgen05.mma.cta_group::2.kind::" KIND " [%1], da, db, %11, p1;\n"                         \
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%12], msk;\n" \
+      "selp.u32 %0, 1, 0, pn;\n"                                                                 \
+      "}\n"                                                                                      \
+      : "=r"(ready)                                                                              \
+      : "r"(tmem_d), "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(b2), "r"(b3),     \
+        "r"(desc_hi), "r"(idesc), "r"(empty_bar), "r"(next_full_bar), "r"(next_parity),          \
+        "n"(kFirstAccumulates ? 1 : 0)                                                           \
+      : "memory")
+  if constexpr (kTf32) {
+    TB200_MMA_STAGE2("tf32");
+  } else {
+    TB200_MMA_STAGE2("f16");
+  }
+#undef TB200_MMA_STAGE2
+  return ready != 0;
+}
+// Arrive on `bar` (same offset in both CTAs of the pair) once every MMA issued so far has retired.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "{\n"
+      ".reg .b16 msk;\n"
+      "mov.b16 msk, 3;\n"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], msk;\n"
+      "}\n" ::"r"(bar)
+      : "memory");
+}
+
+// Producer stage of a CTA pair: both CTAs issue their own copies (their 128 pixels of A, their half of B's
+// rows) into their own shared memory, all signalling the LEADER's full barrier (`full_bar_leader`, a
+// shared::cluster address). No multicast: each CTA fetches what it needs itself. `expect_bytes` is the whole
+// stage of both CTAs for the leader and 0 for the follower (which then skips the arrive).
+__device__ __forceinline__ bool tma_stage_probe_pair(uint32_t a_dst, uint32_t b_dst, uint32_t full_bar_local,
+                                                     uint32_t full_bar_leader, uint32_t expect_bytes,
+                                                     const void* tmap_x, int c, int w, int h, int n, uint16_t off_w,
+                                                     uint16_t off_h, const void* tmap_w, int k0, int n0,
+                                                     uint32_t next_empty_bar, uint32_t next_parity) {
+  uint32_t free_next;
+  asm volatile(
+      "{\n"
+      ".reg .pred pn, pl;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 pn, [%16], %17;\n"
+      "setp.ne.b32 pl, %4, 0;\n"
+      "@pl mbarrier.arrive.expect_tx.shared::cta.b64 _, [%3], %4;\n"
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+      " [%1], [%6, {%7, %8, %9, %10}], [%5], {%11, %12};\n"
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%2], [%13, {%14, %15}], [%5];\n"
+      "selp.u32 %0, 1, 0, pn;\n"
+      "}\n"
+      : "=r"(free_next)
+      : "r"(a_dst), "r"(b_dst), "r"(full_bar_local), "r"(expect_bytes), "r"(full_bar_leader),
+        "l"(reinterpret_cast<uint64_t>(tmap_x)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h),
+        "l"(reinterpret_cast<uint64_t>(tmap_w)), "r"(k0), "r"(n0), "r"(next_empty_bar), "r"(next_parity)
+      : "memory");
+  return free_next != 0;
 }
 
 // One pipeline stage of the TMA producer as a single block, same idea: probe the NEXT slot's empty

@@ -73,7 +73,7 @@ struct DeviceState {
   int num_sms = 0;
   cudaMemPool_t pool = nullptr;
   uint32_t* status = nullptr;  // pinned, mapped: kernels write error codes the host reads directly
-  bool attr_set[3][3] = {};    // [dtype][bn index]
+  bool attr_set[3][3][2] = {};   // [dtype][bn index][single CTA / CTA pair]
   // host-memory path only: copy streams and events for the chunked H2D / compute / D2H pipeline
   static constexpr int kMaxChunks = 16;
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -294,34 +294,56 @@ int pick_bn(long long m_tiles, int k_out, int num_sms) {
   return best;
 }
 
-int pick_stages(int bn) {
-  const int stage_bytes = tb200::kBlockM * tb200::kStageKBytes + bn * tb200::kStageKBytes;
-  const int fixed = tb200::conv_smem_bytes(bn, 0);
+int pick_stages(int bn, bool pair) {
+  const int stage_bytes = tb200::kBlockM * tb200::kStageKBytes + (pair ? bn / 2 : bn) * tb200::kStageKBytes;
+  const int fixed = tb200::conv_smem_bytes(bn, 0, pair);
   int s = (232448 - fixed) / stage_bytes;  // 227 KB opt-in limit per CTA
   return std::min(s, tb200::kMaxStages);
 }
 
-template <typename OutT, int BN>
+template <typename OutT, int BN, bool kPair>
 void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, const CUtensorMap& tw,
                 const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid, int smem,
                 cudaStream_t stream) {
-  auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN>;
-  if (!st.attr_set[dt_idx][bn_idx]) {
+  auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN, kPair>;
+  if (!st.attr_set[dt_idx][bn_idx][kPair ? 1 : 0]) {
     TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
-    st.attr_set[dt_idx][bn_idx] = true;
+    st.attr_set[dt_idx][bn_idx][kPair ? 1 : 0] = true;
   }
-  kern<<<grid, tb200::kNumThreads, smem, stream>>>(tx, tw, to, tr, args);
+  if constexpr (kPair) {
+    // clusters of two CTAs on neighbouring SMs; no multicast is used anywhere in the kernel
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(tb200::kNumThreads);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tx, tw, to, tr, args));
+  } else {
+    kern<<<grid, tb200::kNumThreads, smem, stream>>>(tx, tw, to, tr, args);
+  }
   TB_CUDA(cudaGetLastError());
 }
 
 template <typename OutT>
-void launch_bn(DeviceState& st, int dt_idx, int bn, const CUtensorMap& tx, const CUtensorMap& tw,
+void launch_bn(DeviceState& st, int dt_idx, int bn, bool pair, const CUtensorMap& tx, const CUtensorMap& tw,
                const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid, int smem,
                cudaStream_t stream) {
+  if (pair) {
+    if (bn == 128) launch_one<OutT, 128, true>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream);
+    else launch_one<OutT, 256, true>(st, dt_idx, 2, tx, tw, to, tr, args, grid, smem, stream);
+    return;
+  }
   switch (bn) {
-    case 64: launch_one<OutT, 64>(st, dt_idx, 0, tx, tw, to, tr, args, grid, smem, stream); break;
-    case 128: launch_one<OutT, 128>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream); break;
-    default: launch_one<OutT, 256>(st, dt_idx, 2, tx, tw, to, tr, args, grid, smem, stream); break;
+    case 64: launch_one<OutT, 64, false>(st, dt_idx, 0, tx, tw, to, tr, args, grid, smem, stream); break;
+    case 128: launch_one<OutT, 128, false>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream); break;
+    default: launch_one<OutT, 256, false>(st, dt_idx, 2, tx, tw, to, tr, args, grid, smem, stream); break;
   }
 }
 
@@ -376,7 +398,7 @@ struct NoAllocState {
   bool ready = false;
   int num_sms = 0;
   unsigned char* scratch = nullptr;   // device address of g_static_scratch on this device
-  bool attr_set[3][3] = {};
+  bool attr_set[3][3][2] = {};
 };
 NoAllocState g_noalloc[kMaxDevices];
 
@@ -571,16 +593,23 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   const long long Kgemm = R * Sg * Cg;
 
   // ---- tiles
-  const long long m_tiles = (M + tb200::kBlockM - 1) / tb200::kBlockM;
+  long long m_tiles = (M + tb200::kBlockM - 1) / tb200::kBlockM;
   int bn = pick_bn(m_tiles, static_cast<int>(K), st.num_sms);
   const int forced_bn = env_int("TRACEA_B200_FORCE_BN", 0);
   if (forced_bn == 64 || forced_bn == 128 || forced_bn == 256) bn = forced_bn;
+  // CTA pairs (cta_group::2): a pair of SMs owns a 256 x bn tile and each CTA brings in only half of B's rows
+  // Worth it when the main loop is long enough to dominate the tile (>= 8 k-steps); short-K, epilogue-bound
+  // layers lose more from coupling two SMs' epilogues than they gain. TRACEA_B200_PAIR=0/1 forces the choice.
+  const int pair_env = env_int("TRACEA_B200_PAIR", -1);
+  const bool pair_ok = chunk_bytes == 128 && bn >= 128 && st.num_sms >= 2;
+  const bool pair = pair_ok && (pair_env == 1 || (pair_env != 0 && total_chunks_ll >= 8));
+  if (pair) m_tiles = (M + 2 * tb200::kBlockM - 1) / (2 * tb200::kBlockM);
   const long long n_tiles = (K + bn - 1) / bn;
   if (m_tiles * n_tiles > 0x7fffffffLL) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "too many tiles");
-  int stages = pick_stages(bn);
+  int stages = pick_stages(bn, pair);
   const int forced_stages = env_int("TRACEA_B200_FORCE_STAGES", 0);
   if (forced_stages >= 2 && forced_stages <= stages) stages = forced_stages;
-  const int smem = tb200::conv_smem_bytes(bn, stages);
+  const int smem = tb200::conv_smem_bytes(bn, stages, pair);
 
   // ---- tensor maps
   CUtensorMap tmap_x, tmap_w, tmap_out, tmap_res;
@@ -588,7 +617,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   memset(&tmap_res, 0, sizeof(tmap_res));
   // A 1x1 / stride-1 / unpadded conv over dense NHWC memory is a plain [M][C] x [C][K] GEMM; the
   // tiled map is kept as a cross-check of the im2col path (TRACEA_B200_TILED_A=1).
-  const bool a_tiled = !window && env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
+  const bool a_tiled = !pair && !window && env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
                        p.stride_w == 1 && p.padding_h == 0 && p.padding_w == 0 && x.stride[3] == Cp &&
                        x.stride[2] == W * Cp && x.stride[0] == H * W * Cp;
   if (a_tiled) {
@@ -626,7 +655,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   {
     const cuuint64_t gdim[2] = {(cuuint64_t)Kgemm, (cuuint64_t)K};
     const cuuint64_t gstr[1] = {(cuuint64_t)(Kgemm * es)};
-    const cuuint32_t box[2] = {(cuuint32_t)chunk_elems, (cuuint32_t)bn};
+    const cuuint32_t box[2] = {(cuuint32_t)chunk_elems, (cuuint32_t)(pair ? bn / 2 : bn)};
     const cuuint32_t estr[2] = {1u, 1u};
     CUresult r = g_encode_tiled(&tmap_w, tmap_dtype(x.dtype), 2, const_cast<void*>(w_ptr), gdim, gstr,
                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, tmap_swizzle(chunk_bytes),
@@ -661,7 +690,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   a.num_n_tiles = static_cast<int>(n_tiles);
   a.num_stages = stages;
   const uint32_t fmt = x.dtype == TRACEA_DTYPE_FLOAT16 ? 0u : (x.dtype == TRACEA_DTYPE_BFLOAT16 ? 1u : 2u);
-  a.idesc = tb200::ptx::make_idesc(fmt, tb200::kBlockM, bn);
+  a.idesc = tb200::ptx::make_idesc(fmt, pair ? 2 * tb200::kBlockM : tb200::kBlockM, bn);
   // K-major operand descriptors. Swizzled rows of chunk_bytes: 8-row groups are 8*chunk_bytes apart
   // (SBO) and one MMA (32 B of K) stays inside a row. Unswizzled 16-byte chunks: an 8-row x 16 B core
   // matrix is 128 contiguous bytes (SBO) and the MMA's second K half is the next chunk (LBO).
@@ -747,16 +776,17 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
 #endif
 
   const long long tiles = m_tiles * n_tiles;
-  const int grid = static_cast<int>(std::min<long long>(tiles, st.num_sms));
+  const int grid = pair ? 2 * static_cast<int>(std::min<long long>(tiles, st.num_sms / 2))
+                        : static_cast<int>(std::min<long long>(tiles, st.num_sms));
   switch (x.dtype) {
     case TRACEA_DTYPE_BFLOAT16:
-      launch_bn<__nv_bfloat16>(st, 0, bn, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
+      launch_bn<__nv_bfloat16>(st, 0, bn, pair, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
       break;
     case TRACEA_DTYPE_FLOAT16:
-      launch_bn<__half>(st, 1, bn, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
+      launch_bn<__half>(st, 1, bn, pair, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
       break;
     default:
-      launch_bn<float>(st, 2, bn, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
+      launch_bn<float>(st, 2, bn, pair, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
       break;
   }
 }
