@@ -157,8 +157,9 @@ constexpr int kStagingDepth = 2;
 constexpr int kNumEpilogueWarps = 8;
 constexpr int kStagingBytes = kNumEpilogueWarps * kStagingDepth * kStagingBoxBytes;
 // `pair`: two CTAs on neighbouring SMs work on one 256-row tile and each holds only half of B's rows.
-__host__ __device__ constexpr int conv_smem_bytes(int bn, int stages, bool pair = false) {
-  return stages * (kBlockM * kStageKBytes + (pair ? bn / 2 : bn) * kStageKBytes) + kStagingBytes +
+// `rows2`: one CTA owns a 256-row tile (two 128-row blocks of A per stage against one B).
+__host__ __device__ constexpr int conv_smem_bytes(int bn, int stages, bool pair = false, bool rows2 = false) {
+  return stages * ((rows2 ? 2 : 1) * kBlockM * kStageKBytes + (pair ? bn / 2 : bn) * kStageKBytes) + kStagingBytes +
          kNumEpilogueWarps * bn * 4 + 512 + 1024;
 }
 
@@ -300,7 +301,10 @@ __device__ __noinline__ void epilogue_block_generic(const ConvKernelArgs& args, 
 // kPair: launched as clusters of two CTAs (cta_group::2). The pair owns a 256 x BN tile: each CTA loads its own
 // 128 pixels of A and its own half of B's rows (no multicast), the leader CTA issues M = 256 MMAs that span both
 // SMs, each CTA drains its own 128 TMEM lanes. Per CTA this halves the B bytes brought in per MMA.
-template <typename OutT, int BN, bool kPair>
+// kRows2 (single CTA, narrow outputs): the CTA owns a 256 x BN tile as two 128-row blocks with one accumulator
+// each; a stage carries both A blocks and one B, i.e. eight MMAs per barrier probe instead of four, and the two
+// epilogue groups drain the two halves of the same tile instead of alternate tiles.
+template <typename OutT, int BN, bool kPair, bool kRows2>
 __global__ void __launch_bounds__(kNumThreads, 1)
 conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ CUtensorMap tmap_w,
@@ -308,17 +312,21 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ CUtensorMap tmap_res,
                           const __grid_constant__ ConvKernelArgs args) {
   using namespace ptx;
-  constexpr uint32_t kABytes = kBlockM * kStageKBytes;   // 16 KB
+  static_assert(!(kPair && kRows2), "one tiling variant at a time");
+  static_assert(!kRows2 || BN <= 128, "two accumulator pairs of a 256-row tile must fit 512 TMEM columns");
+  constexpr uint32_t kABlockBytes = kBlockM * kStageKBytes;            // one 128-pixel block of A: 16 KB
+  constexpr uint32_t kABytes = (kRows2 ? 2u : 1u) * kABlockBytes;
   constexpr uint32_t kBRows = kPair ? BN / 2 : BN;       // rows of B this CTA keeps in shared memory
   constexpr uint32_t kBBytes = kBRows * kStageKBytes;
   constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  constexpr int kTileM = kPair ? 2 * kBlockM : kBlockM;  // output pixels per tile (of the pair)
+  constexpr int kTileM = (kPair || kRows2) ? 2 * kBlockM : kBlockM;   // output pixels per tile
   const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0u;
   // tiles are dealt to CTAs (or CTA pairs) round robin
   const int worker = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int num_workers = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-  constexpr uint32_t kTmemCols = 2 * BN;                 // two accumulators: 128, 256 or 512 columns
+  constexpr uint32_t kAccCols = (kRows2 ? 2 : 1) * BN;   // TMEM columns of one tile's accumulator(s)
+  constexpr uint32_t kTmemCols = 2 * kAccCols;           // double-buffered: 128, 256 or 512 columns
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
 
   extern __shared__ uint8_t smem_raw[];
@@ -350,7 +358,8 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), kPair ? 8 : 4);   // one arrival per epilogue warp (of both CTAs of a pair)
+      // one arrival per epilogue warp that drains the buffer: 4, or 8 when both groups / both CTAs of a pair do
+      mbar_init(tempty_bar(b), (kPair || kRows2) ? 8 : 4);
     }
     for (int q = 0; q < kNumEpilogueWarps; ++q)
       for (int b = 0; b < kStagingDepth; ++b) mbar_init(res_bar(q, b), 1);
@@ -452,6 +461,14 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int w_start = q0 * args.stride_w - args.pad_w;
         const int h_start = p0 * args.stride_h - args.pad_h;
         const int n_coord = n_tile * BN + static_cast<int>(cta_rank * kBRows);   // this CTA's rows of B
+        int w_start1 = 0, h_start1 = 0, img1 = 0;   // start pixel of the tile's second 128-row block
+        if constexpr (kRows2) {
+          const int m1 = m0 + kBlockM;
+          const int t1 = m1 / args.Wo;
+          w_start1 = (m1 % args.Wo) * args.stride_w - args.pad_w;
+          h_start1 = (t1 % args.Ho) * args.stride_h - args.pad_h;
+          img1 = t1 / args.Ho;
+        }
         if (one_chunk) {
           // common case: one 128-byte chunk per stage = 64 (16-bit) or 32 (fp32) channels of one tap
           int c_coord = 0, k_coord = 0, tap_s = 0;
@@ -474,6 +491,11 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                full_leader0 + (full_addr - full_bar0), leader ? 2u * kStageBytes : 0u,
                                                &tmap_x, c_coord, w_start, h_start, img0, (uint16_t)off_w,
                                                (uint16_t)off_h, &tmap_w, k_coord, n_coord, nempty, nphase ^ 1u);
+            } else if constexpr (kRows2) {
+              next_free = tma_stage_probe_rows2(stage_addr, stage_addr + kABlockBytes, stage_addr + kABytes, full_addr,
+                                                kStageBytes, &tmap_x, c_coord, w_start, h_start, img0, w_start1,
+                                                h_start1, img1, (uint16_t)off_w, (uint16_t)off_h, &tmap_w, k_coord,
+                                                n_coord, nempty, nphase ^ 1u);
             } else {
               next_free = tma_stage_probe(stage_addr, stage_addr + kABytes, full_addr, kStageBytes, &tmap_x, c_coord,
                                           w_start, h_start, img0, (uint16_t)off_w, (uint16_t)off_h, &tmap_w, k_coord,
@@ -586,7 +608,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         TB200_PROF_ADD(prof_wtmem, tw0);
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf) * kAccCols;
         for (int it = 0; it < k_iters; ++it) {
           TB200_PROF_T(tw1);
           if (!stage_ready && !mbar_wait_bounded(full_addr, phase, abort_p, kWaitLimitCycles)) {
@@ -600,7 +622,18 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (n_off == ring_units) { n_off = 0; nfull = full_bar0; nempty = empty_bar0; nphase ^= 1u; }
           tc_fence_after();
           bool next_ready;
-          if constexpr (kPair) {
+          if constexpr (kRows2) {
+            if (it == 0)
+              next_ready = mma_stage8_probe<kTf32, false>(d_tmem, d_tmem + BN, a_k[0] + s_off, a_k[1] + s_off,
+                                                          a_k[2] + s_off, a_k[3] + s_off, kABlockBytes >> 4,
+                                                          b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off, b_k[3] + s_off,
+                                                          desc_hi, idesc, empty_addr, nfull, nphase);
+            else
+              next_ready = mma_stage8_probe<kTf32, true>(d_tmem, d_tmem + BN, a_k[0] + s_off, a_k[1] + s_off,
+                                                         a_k[2] + s_off, a_k[3] + s_off, kABlockBytes >> 4,
+                                                         b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off, b_k[3] + s_off,
+                                                         desc_hi, idesc, empty_addr, nfull, nphase);
+          } else if constexpr (kPair) {
             if (it == 0)
               next_ready = mma_stage4_probe_pair<kTf32, false>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
                                                                a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off,
@@ -675,26 +708,28 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         bias_next[j] = b;
       }
     };
-    // this group's tiles: worker + (egroup + 2 i) * num_workers
-    const int etile0 = worker + egroup * num_workers;
-    const int estride = 2 * num_workers;
+    // this group's tiles: worker + (egroup + 2 i) * num_workers -- or, with two-row-block tiles, every tile of
+    // the worker, of which the group takes the 128-row block `egroup`
+    const int etile0 = kRows2 ? worker : worker + egroup * num_workers;
+    const int estride = kRows2 ? num_workers : 2 * num_workers;
     const int estep_m = estride / args.num_n_tiles, estep_n = estride % args.num_n_tiles;
     if (etile0 < num_tiles) fetch_bias(etile0 % args.num_n_tiles);
-    int local_tile = egroup;
+    int local_tile = kRows2 ? 0 : egroup;
     bool ok = true;
     long long prof_wacc = 0, prof_wres = 0, prof_ld = 0, prof_math = 0, prof_stage = 0, prof_wstore = 0;
     (void)prof_wacc; (void)prof_wres; (void)prof_ld; (void)prof_math; (void)prof_stage; (void)prof_wstore;
     TB200_PROF_T(prof_t0);
     int m_tile = etile0 / args.num_n_tiles - estep_m, n_tile = etile0 % args.num_n_tiles - estep_n;
     const bool need_coords = !args.out_tma || (res != nullptr && !res_tma);
-    for (int tile = etile0; tile < num_tiles && ok; tile += estride, local_tile += 2) {
+    for (int tile = etile0; tile < num_tiles && ok; tile += estride, local_tile += (kRows2 ? 1 : 2)) {
       n_tile += estep_n; m_tile += estep_m;
       if (n_tile >= args.num_n_tiles) { n_tile -= args.num_n_tiles; ++m_tile; }
       else if (n_tile < 0) { n_tile += args.num_n_tiles; --m_tile; }
-      const int buf = egroup;
+      const int buf = kRows2 ? (local_tile & 1) : egroup;
       const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
       const int n_base = n_tile * BN;
-      const int m_row0 = m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM + quarter * 32;
+      const int row_block = kPair ? static_cast<int>(cta_rank) : (kRows2 ? egroup : 0);   // which 128 rows of the tile
+      const int m_row0 = m_tile * kTileM + row_block * kBlockM + quarter * 32;
 
       // this warp's fp32 copy of the tile's bias (zeros when there is none / past K_out); the values
       // were fetched into registers during the previous tile, and the next tile's are fetched now
@@ -711,7 +746,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         fetch_bias(nn);
       }
 
-      const int m = m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM + row;
+      const int m = m_tile * kTileM + row_block * kBlockM + row;
       const bool row_ok = m < args.M;
       long long out_off = 0, res_off = 0;
       if (need_coords) {   // only the per-lane store / load paths need (n, ho, wo); the TMA paths do not
@@ -744,7 +779,8 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
       tc_fence_after();
       const uint32_t taddr0 =
-          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf) * kAccCols +
+          (kRows2 ? static_cast<uint32_t>(egroup * BN) : 0u);
 
 #pragma unroll 1
       for (int g = 0; g < kGroups; ++g) {

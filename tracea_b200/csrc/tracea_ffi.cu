@@ -73,7 +73,7 @@ struct DeviceState {
   int num_sms = 0;
   cudaMemPool_t pool = nullptr;
   uint32_t* status = nullptr;  // pinned, mapped: kernels write error codes the host reads directly
-  bool attr_set[3][3][2] = {};   // [dtype][bn index][single CTA / CTA pair]
+  bool attr_set[3][3][3] = {};   // [dtype][bn index][tiling: single CTA / CTA pair / two row blocks]
   // host-memory path only: copy streams and events for the chunked H2D / compute / D2H pipeline
   static constexpr int kMaxChunks = 16;
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -294,21 +294,22 @@ int pick_bn(long long m_tiles, int k_out, int num_sms) {
   return best;
 }
 
-int pick_stages(int bn, bool pair) {
-  const int stage_bytes = tb200::kBlockM * tb200::kStageKBytes + (pair ? bn / 2 : bn) * tb200::kStageKBytes;
-  const int fixed = tb200::conv_smem_bytes(bn, 0, pair);
+int pick_stages(int bn, bool pair, bool rows2) {
+  const int stage_bytes = tb200::conv_smem_bytes(bn, 1, pair, rows2) - tb200::conv_smem_bytes(bn, 0, pair, rows2);
+  const int fixed = tb200::conv_smem_bytes(bn, 0, pair, rows2);
   int s = (232448 - fixed) / stage_bytes;  // 227 KB opt-in limit per CTA
   return std::min(s, tb200::kMaxStages);
 }
 
-template <typename OutT, int BN, bool kPair>
+template <typename OutT, int BN, bool kPair, bool kRows2 = false>
 void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, const CUtensorMap& tw,
                 const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid, int smem,
                 cudaStream_t stream) {
-  auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN, kPair>;
-  if (!st.attr_set[dt_idx][bn_idx][kPair ? 1 : 0]) {
+  auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN, kPair, kRows2>;
+  constexpr int kVariant = kPair ? 1 : (kRows2 ? 2 : 0);
+  if (!st.attr_set[dt_idx][bn_idx][kVariant]) {
     TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
-    st.attr_set[dt_idx][bn_idx][kPair ? 1 : 0] = true;
+    st.attr_set[dt_idx][bn_idx][kVariant] = true;
   }
   if constexpr (kPair) {
     // clusters of two CTAs on neighbouring SMs; no multicast is used anywhere in the kernel
@@ -332,9 +333,14 @@ void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, 
 }
 
 template <typename OutT>
-void launch_bn(DeviceState& st, int dt_idx, int bn, bool pair, const CUtensorMap& tx, const CUtensorMap& tw,
-               const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid, int smem,
-               cudaStream_t stream) {
+void launch_bn(DeviceState& st, int dt_idx, int bn, bool pair, bool rows2, const CUtensorMap& tx,
+               const CUtensorMap& tw, const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid,
+               int smem, cudaStream_t stream) {
+  if (rows2) {
+    if (bn == 64) launch_one<OutT, 64, false, true>(st, dt_idx, 0, tx, tw, to, tr, args, grid, smem, stream);
+    else launch_one<OutT, 128, false, true>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream);
+    return;
+  }
   if (pair) {
     if (bn == 128) launch_one<OutT, 128, true>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream);
     else launch_one<OutT, 256, true>(st, dt_idx, 2, tx, tw, to, tr, args, grid, smem, stream);
@@ -398,7 +404,7 @@ struct NoAllocState {
   bool ready = false;
   int num_sms = 0;
   unsigned char* scratch = nullptr;   // device address of g_static_scratch on this device
-  bool attr_set[3][3][2] = {};
+  bool attr_set[3][3][3] = {};
 };
 NoAllocState g_noalloc[kMaxDevices];
 
@@ -601,15 +607,19 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   // Worth it when the main loop is long enough to dominate the tile (>= 8 k-steps); short-K, epilogue-bound
   // layers lose more from coupling two SMs' epilogues than they gain. TRACEA_B200_PAIR=0/1 forces the choice.
   const int pair_env = env_int("TRACEA_B200_PAIR", -1);
-  const bool pair_ok = chunk_bytes == 128 && bn >= 128 && st.num_sms >= 2;
+  const bool pair_ok = chunk_bytes == 128 && bn == 256 && st.num_sms >= 2;
   const bool pair = pair_ok && (pair_env == 1 || (pair_env != 0 && total_chunks_ll >= 8));
-  if (pair) m_tiles = (M + 2 * tb200::kBlockM - 1) / (2 * tb200::kBlockM);
+  // Two row blocks per CTA for narrow outputs (bn <= 128): twice the tensor work per barrier probe and per tile.
+  const int rows2_env = env_int("TRACEA_B200_ROWS2", -1);
+  const bool rows2 = !pair && chunk_bytes == 128 && bn <= 128 && rows2_env != 0 &&
+                     (rows2_env == 1 || (total_chunks_ll >= 7 && m_tiles >= 2LL * st.num_sms));
+  if (pair || rows2) m_tiles = (M + 2 * tb200::kBlockM - 1) / (2 * tb200::kBlockM);
   const long long n_tiles = (K + bn - 1) / bn;
   if (m_tiles * n_tiles > 0x7fffffffLL) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "too many tiles");
-  int stages = pick_stages(bn, pair);
+  int stages = pick_stages(bn, pair, rows2);
   const int forced_stages = env_int("TRACEA_B200_FORCE_STAGES", 0);
   if (forced_stages >= 2 && forced_stages <= stages) stages = forced_stages;
-  const int smem = tb200::conv_smem_bytes(bn, stages, pair);
+  const int smem = tb200::conv_smem_bytes(bn, stages, pair, rows2);
 
   // ---- tensor maps
   CUtensorMap tmap_x, tmap_w, tmap_out, tmap_res;
@@ -617,7 +627,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   memset(&tmap_res, 0, sizeof(tmap_res));
   // A 1x1 / stride-1 / unpadded conv over dense NHWC memory is a plain [M][C] x [C][K] GEMM; the
   // tiled map is kept as a cross-check of the im2col path (TRACEA_B200_TILED_A=1).
-  const bool a_tiled = !pair && !window && env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
+  const bool a_tiled = !pair && !rows2 && !window && env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
                        p.stride_w == 1 && p.padding_h == 0 && p.padding_w == 0 && x.stride[3] == Cp &&
                        x.stride[2] == W * Cp && x.stride[0] == H * W * Cp;
   if (a_tiled) {
@@ -780,13 +790,13 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
                         : static_cast<int>(std::min<long long>(tiles, st.num_sms));
   switch (x.dtype) {
     case TRACEA_DTYPE_BFLOAT16:
-      launch_bn<__nv_bfloat16>(st, 0, bn, pair, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
+      launch_bn<__nv_bfloat16>(st, 0, bn, pair, rows2, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
       break;
     case TRACEA_DTYPE_FLOAT16:
-      launch_bn<__half>(st, 1, bn, pair, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
+      launch_bn<__half>(st, 1, bn, pair, rows2, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
       break;
     default:
-      launch_bn<float>(st, 2, bn, pair, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
+      launch_bn<float>(st, 2, bn, pair, rows2, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
       break;
   }
 }
