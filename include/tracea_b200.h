@@ -143,6 +143,72 @@ TraceaStatus tracea_conv2d_noalloc(TraceaTensorView x, TraceaTensorView w, const
                                    const TraceaTensorView *residual, TraceaTensorView *out,
                                    TraceaConv2dParams params);
 
+/* ---- the operators either side of the conv path, run on the same kernel ------------------------------- */
+
+/* include/tracea.hpp:84-87. */
+typedef struct {
+  TraceaEpilogueKind epilogue;
+  void *stream;
+} TraceaGemmParams;
+
+/* c = epilogue(a[M,K] * b[K,N]): replaces include/tracea.hpp:139-144 and src/interface/c_bindings.rs:375-440.
+ * Rank-2 views, strides in elements (NULL = row-major). It runs as the 1x1 convolution it is: `a` rows are the
+ * pixels, `b` columns the output channels. The zero-copy form is a with stride[1] == 1 and b with stride[0] == 1
+ * and stride[1] == K (memory [N][K], e.g. a transposed view of a Linear layer's weight, or the buffer
+ * tracea_gemm_prepack_b wrote); a row-major b is transposed into scratch on every call. bias: rank-1, length N;
+ * residual: [M,N], dtype of c. Dtypes as tracea_conv2d (fp32 runs as TF32; the reference's entry took fp16 only).
+ * rank != 2 or a shape mismatch -> INVALID_PARAMS. */
+TraceaStatus tracea_gemm(TraceaTensorView a, TraceaTensorView b, const TraceaTensorView *bias,
+                         const TraceaTensorView *residual, TraceaTensorView *c, TraceaGemmParams params);
+
+/* include/tracea.hpp:118-131. */
+typedef struct {
+  uint32_t stride_h;
+  uint32_t stride_w;
+  uint32_t padding_h;
+  uint32_t padding_w;
+  uint32_t output_padding_h;
+  uint32_t output_padding_w;
+  uint32_t dilation_h;
+  uint32_t dilation_w;
+  uint32_t groups;
+  TraceaEpilogueKind epilogue;
+  void *stream;
+} TraceaConvTranspose2dParams;
+
+/* out = epilogue(conv_transpose2d(x, w)): replaces include/tracea.hpp:133-137 and
+ * src/interface/c_bindings.rs:292-372. Shapes are the ones that entry reads (c_bindings.rs:301-311;
+ * tracea-python/python/tracea/ops.py:72-88): x [N,H,W,C], w [K,R,S,C], out and residual [N,Ho,Wo,K] with
+ * Ho = (H-1)*stride_h - 2*padding_h + R + output_padding_h; strides in elements decide the memory layout
+ * (NULL = row-major, i.e. NHWC / KRSC memory). The reference's kernel reads its weights as [C*R*S][K] memory
+ * (src/emitter/conv_transpose.rs:232-243): pass that buffer as shape [K,R,S,C] with strides {1, S*K, K, R*S*K}.
+ * out[n,ho,wo,k] = sum over (hi,r), (wi,s), c with ho = hi*stride_h - padding_h + r of x[n,hi,wi,c]*w[k,r,s,c]
+ * (examples/verify_conv_transpose.rs:12-52). It runs as stride_h*stride_w stride-1 convolutions, one per output
+ * phase, each over the filter taps that reach that phase.
+ * dilation != 1 or groups != 1 -> UNSUPPORTED_CONFIG (the reference ignores both fields); output_padding must be
+ * smaller than the stride; other validation as tracea_conv2d. Device tensors and host tensors (device_id -1,
+ * staged through the current GPU) are accepted. */
+TraceaStatus tracea_conv_transpose2d(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView *b,
+                                     const TraceaTensorView *residual, TraceaTensorView *out,
+                                     TraceaConvTranspose2dParams params);
+
+/* Weight prepacking, so that the documented OIHW / row-major surface costs nothing in steady state. No
+ * counterpart in the reference, whose kernels fix one weight layout per back end (src/emitter/cuda/conv.rs:248-266).
+ *
+ * tracea_conv2d_prepack writes w (logical [K,C,R,S], any strides, device memory) into `dst` as dense
+ * [K][R][S][Cp] memory, Cp = C rounded up to 16 bytes' worth of elements with zero fill, on `stream`, and fills
+ * `packed_shape` / `packed_stride` with the logical [K,Cp,R,S] view of dst to hand to tracea_conv2d (which then
+ * reads it in place). When Cp != C the activations passed with it must carry Cp channels too (zero padded).
+ * tracea_gemm_prepack_b does the same for b[K,N]: dst becomes [N][K] memory and packed_stride = {1, K}.
+ * `dst_bytes` must be at least tracea_conv2d_prepack_bytes(w) / tracea_gemm_prepack_b_bytes(b) (0 on a bad view);
+ * dst must be 16-byte aligned and on w.device_id. */
+uint64_t tracea_conv2d_prepack_bytes(TraceaTensorView w);
+TraceaStatus tracea_conv2d_prepack(TraceaTensorView w, void *dst, uint64_t dst_bytes, uint64_t packed_shape[4],
+                                   int64_t packed_stride[4], void *stream);
+uint64_t tracea_gemm_prepack_b_bytes(TraceaTensorView b);
+TraceaStatus tracea_gemm_prepack_b(TraceaTensorView b, void *dst, uint64_t dst_bytes, int64_t packed_stride[2],
+                                   void *stream);
+
 /* Thread-local last error text: tracea-ffi/src/lib.rs:87-109. Returns bytes copied (without the
  * terminating NUL), -1 when buf is NULL or len is 0. */
 int32_t tracea_get_last_error(uint8_t *buf, size_t len);

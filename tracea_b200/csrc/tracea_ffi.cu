@@ -432,12 +432,22 @@ NoAllocState& noalloc_state(int dev) {
 }
 
 // ------------------------------------------------------------------ the device path
+// The conv geometry the kernel runs: the public parameters plus a separate padding behind the last row /
+// column. padding_h / padding_w pad in front; the output extents are out.shape[2], out.shape[3] and must equal
+// (H + padding_h + pad_h_hi - dilation_h*(R-1) - 1) / stride_h + 1 (same for w). tracea_conv2d always pads
+// symmetrically; the phases of a transposed convolution do not.
+struct CoreParams : TraceaConv2dParams {
+  long long pad_h_hi = 0, pad_w_hi = 0;
+  CoreParams() : TraceaConv2dParams() {}
+  CoreParams(const TraceaConv2dParams& p) : TraceaConv2dParams(p), pad_h_hi(p.padding_h), pad_w_hi(p.padding_w) {}
+};
+
 // All pointers are device pointers on `dev`. x: [N,C,H,W], w: [K,C,R,S], out: [N,K,Ho,Wo] (logical).
 void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const View4& w_in, const View4* bias,
-                 const View4* residual, const View4& out, const TraceaConv2dParams& p, const Epilogue& epi);
+                 const View4* residual, const View4& out, const CoreParams& p, const Epilogue& epi);
 
 void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* bias,
-                   const View4* residual, const View4& out, const TraceaConv2dParams& p,
+                   const View4* residual, const View4& out, const CoreParams& p,
                    const Epilogue& epi) {
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceGuard guard(dev);
@@ -456,7 +466,7 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
 // Same device path with every staging buffer carved out of the library's static scratch: no call
 // below this point allocates or frees device or pinned memory.
 void conv2d_device_noalloc(int dev, const View4& x_in, const View4& w_in, const View4* bias,
-                           const View4* residual, const View4& out, const TraceaConv2dParams& p,
+                           const View4* residual, const View4& out, const CoreParams& p,
                            const Epilogue& epi) {
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceGuard guard(dev);
@@ -473,7 +483,7 @@ void conv2d_device_noalloc(int dev, const View4& x_in, const View4& w_in, const 
 }
 
 void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const View4& w_in, const View4* bias,
-                 const View4* residual, const View4& out, const TraceaConv2dParams& p, const Epilogue& epi) {
+                 const View4* residual, const View4& out, const CoreParams& p, const Epilogue& epi) {
   cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
   // staging comes from the stream-ordered pool, or from the static scratch for the no-alloc entry
   auto staging = [&](Scratch& s, size_t bytes, const char* what) -> void* {
@@ -492,7 +502,8 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "stride > 8 is not supported (TMA traversal stride limit)");
   if ((S - 1) * p.dilation_w > 255 || (R - 1) * p.dilation_h > 255)
     TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "filter extent > 256 is not supported (TMA im2col offset limit)");
-  if (p.padding_h > 32767 || p.padding_w > 32767)
+  if (p.padding_h > 32767 || p.padding_w > 32767 || p.pad_h_hi > 32767 || p.pad_w_hi > 32767 || p.pad_h_hi < 0 ||
+      p.pad_w_hi < 0)
     TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "padding > 32767 is not supported");
 
   const int vec_elems = 16 / es;
@@ -502,7 +513,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   // horizontal padding materialised; one filter row of a pixel is then 8 adjacent pixels = one 128-byte
   // k-chunk, fetched by a single im2col copy over an overlapping view (pixel pitch 16 B, "pixel" size 128 B).
   const bool window = Cp * es == 16 && S > 1 && S <= 8 && p.dilation_w == 1 && W + 2LL * p.padding_w < (1LL << 30) &&
-                      env_int("TRACEA_B200_NO_WINDOW", 0) == 0;
+                      p.pad_w_hi == (long long)p.padding_w && env_int("TRACEA_B200_NO_WINDOW", 0) == 0;
   const long long Wpitch = W + 2LL * p.padding_w + 8;   // row pitch of the padded copy, in pixels
 
   // ---- activations: consume channels-last memory directly, otherwise transpose into scratch
@@ -564,7 +575,20 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     void* w_stage = staging(w_scratch, static_cast<size_t>(total) * es, "the repacked weights");
     const int threads = 256;
     const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
-    if (es == 2)
+    if (R == 1 && Sd == 1 && (Cp + 31) / 32 <= 65535) {
+      // a 1x1 filter is a [K][C] matrix: the tiled transpose keeps both sides coalesced when w arrives
+      // C-major (a row-major GEMM B operand)
+      dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>((Cp + 31) / 32), 1u);
+      dim3 block(32, 8);
+      if (es == 2)
+        tb200::to_channels_last_kernel<uint16_t><<<grid, block, 0, stream>>>(
+            static_cast<const uint16_t*>(w_in.ptr), static_cast<uint16_t*>(w_stage), (int)C, 1, (int)K, (int)Cp, 0LL,
+            w_in.stride[1], 0LL, w_in.stride[0]);
+      else
+        tb200::to_channels_last_kernel<uint32_t><<<grid, block, 0, stream>>>(
+            static_cast<const uint32_t*>(w_in.ptr), static_cast<uint32_t*>(w_stage), (int)C, 1, (int)K, (int)Cp, 0LL,
+            w_in.stride[1], 0LL, w_in.stride[0]);
+    } else if (es == 2)
       tb200::pack_weights_krsc_kernel<uint16_t><<<blocks, threads, 0, stream>>>(
           static_cast<const uint16_t*>(w_in.ptr), static_cast<uint16_t*>(w_stage), total, (int)C,
           (int)R, (int)S, (int)Sd, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
@@ -628,7 +652,8 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   // A 1x1 / stride-1 / unpadded conv over dense NHWC memory is a plain [M][C] x [C][K] GEMM; the
   // tiled map is kept as a cross-check of the im2col path (TRACEA_B200_TILED_A=1).
   const bool a_tiled = !pair && !rows2 && !window && env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
-                       p.stride_w == 1 && p.padding_h == 0 && p.padding_w == 0 && x.stride[3] == Cp &&
+                       p.stride_w == 1 && p.padding_h == 0 && p.padding_w == 0 && p.pad_h_hi == 0 && p.pad_w_hi == 0 &&
+                       x.stride[3] == Cp &&
                        x.stride[2] == W * Cp && x.stride[0] == H * W * Cp;
   if (a_tiled) {
     const cuuint64_t gdim[2] = {(cuuint64_t)Cp, (cuuint64_t)M};
@@ -647,8 +672,8 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     const cuuint64_t gstr[3] = {(cuuint64_t)(x.stride[3] * es), (cuuint64_t)(x.stride[2] * es),
                                 (cuuint64_t)(x.stride[0] * es)};
     const int lower[2] = {window ? 0 : -(int)p.padding_w, -(int)p.padding_h};
-    const int upper[2] = {window ? -(int)(S - 1) : (int)p.padding_w - (int)((S - 1) * p.dilation_w),
-                          (int)p.padding_h - (int)((R - 1) * p.dilation_h)};
+    const int upper[2] = {window ? -(int)(S - 1) : (int)p.pad_w_hi - (int)((S - 1) * p.dilation_w),
+                          (int)p.pad_h_hi - (int)((R - 1) * p.dilation_h)};
     const cuuint32_t estr[4] = {1u, p.stride_w, p.stride_h, 1u};
     CUresult r = g_encode_im2col(&tmap_x, tmap_dtype(x.dtype), 4, x.ptr, gdim, gstr, lower, upper,
                                  (cuuint32_t)chunk_elems, (cuuint32_t)tb200::kBlockM, estr,
@@ -996,6 +1021,394 @@ void conv2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, cons
   if (code != 0u) TB_FAIL(TRACEA_CUDA_ERROR, "conv kernel gave up a bounded wait (code %u)", code);
 }
 
+// ------------------------------------------------------------------ GEMM: the 1x1 convolution it is
+struct Rank2 {
+  long long shape[2];
+  long long stride[2];
+};
+
+Rank2 load_rank2(const TraceaTensorView& v, const char* name) {
+  if (v.rank != 2) TB_FAIL(TRACEA_INVALID_PARAMS, "Expected 2D tensors: %s has rank %u", name, v.rank);
+  if (v.shape == nullptr) TB_FAIL(TRACEA_INVALID_PARAMS, "%s: shape array is NULL", name);
+  Rank2 r;
+  for (int i = 0; i < 2; ++i) {
+    r.shape[i] = static_cast<long long>(v.shape[i]);
+    if (r.shape[i] < 0 || r.shape[i] > 0x7fffffffLL)
+      TB_FAIL(TRACEA_INVALID_PARAMS, "%s: shape[%d] = %llu is out of range", name, i, (unsigned long long)v.shape[i]);
+  }
+  r.stride[0] = v.stride != nullptr ? v.stride[0] : r.shape[1];
+  r.stride[1] = v.stride != nullptr ? v.stride[1] : 1;
+  if (r.stride[0] < 0 || r.stride[1] < 0) TB_FAIL(TRACEA_INVALID_PARAMS, "%s: negative stride", name);
+  return r;
+}
+
+// A rank-2 [rows, cols] matrix as the rank-4 view {1, cols, 1, rows}: rows are pixels along W, cols channels.
+struct AsConvView {
+  uint64_t shape[4];
+  int64_t stride[4];
+  TraceaTensorView view;
+  AsConvView(const TraceaTensorView& v, const Rank2& r) {
+    shape[0] = 1; shape[1] = (uint64_t)r.shape[1]; shape[2] = 1; shape[3] = (uint64_t)r.shape[0];
+    stride[1] = r.stride[1];
+    stride[3] = r.stride[0];
+    stride[2] = stride[0] = r.stride[0] * r.shape[0];
+    view = v;
+    view.rank = 4;
+    view.shape = shape;
+    view.stride = stride;
+  }
+};
+
+void gemm_checked(const TraceaTensorView& av, const TraceaTensorView& bv, const TraceaTensorView* biasv,
+                  const TraceaTensorView* rv, TraceaTensorView* cv, const TraceaGemmParams& gp) {
+  if (av.ptr == nullptr || bv.ptr == nullptr || cv == nullptr || cv->ptr == nullptr)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "Null pointer in input tensors");
+  const Rank2 a = load_rank2(av, "a"), b = load_rank2(bv, "b"), c = load_rank2(*cv, "c");
+  const long long M = a.shape[0], K = a.shape[1], N = b.shape[1];
+  if (b.shape[0] != K)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "Inner dimension mismatch: a is [%lld,%lld], b is [%lld,%lld]", M, K, b.shape[0], N);
+  if (c.shape[0] != M || c.shape[1] != N)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "c shape [%lld,%lld] does not match expected [%lld,%lld]", c.shape[0], c.shape[1], M, N);
+  if (K == 0 || N == 0) TB_FAIL(TRACEA_INVALID_PARAMS, "K = %lld, N = %lld: both must be positive", K, N);
+  Rank2 r2 = c;
+  if (rv != nullptr) {
+    if (rv->ptr == nullptr) TB_FAIL(TRACEA_INVALID_PARAMS, "residual view has a NULL pointer");
+    r2 = load_rank2(*rv, "residual");
+    if (r2.shape[0] != M || r2.shape[1] != N) TB_FAIL(TRACEA_INVALID_PARAMS, "residual shape must equal the c shape");
+  }
+  if (M == 0) {   // nothing to compute; still reject what tracea_conv2d would reject
+    if (elem_size(av.dtype) == 0) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "Unsupported dtype %s", dtype_name(av.dtype));
+    return;
+  }
+
+  AsConvView x4(av, a), o4(*cv, c);
+  // b[K,N] is the filter bank w[N, K, 1, 1]: output channel n reads column n of b
+  uint64_t wshape[4] = {(uint64_t)N, (uint64_t)K, 1, 1};
+  int64_t wstride[4] = {b.stride[1], b.stride[0], 0, 0};
+  if (b.stride[0] == 1) wstride[2] = wstride[3] = K;
+  TraceaTensorView w4 = bv;
+  w4.rank = 4;
+  w4.shape = wshape;
+  w4.stride = wstride;
+  TraceaTensorView res_view;
+  AsConvView* r4 = nullptr;
+  AsConvView r4_storage(rv != nullptr ? *rv : *cv, r2);
+  if (rv != nullptr) {
+    r4 = &r4_storage;
+    res_view = r4->view;
+  }
+  TraceaConv2dParams p;
+  p.stride_h = p.stride_w = 1;
+  p.padding_h = p.padding_w = 0;
+  p.dilation_h = p.dilation_w = 1;
+  p.groups = 1;
+  p.epilogue = gp.epilogue;
+  p.stream = gp.stream;
+  try {
+    conv2d_checked(x4.view, w4, biasv, r4 != nullptr ? &res_view : nullptr, &o4.view, p);
+  } catch (const StatusError&) {
+    g_last_error = "tracea_gemm (run as a 1x1 conv: a is x, b is w, c is out): " + g_last_error;
+    throw;
+  }
+}
+
+// ------------------------------------------------------------------ ConvTranspose2d: one stride-1 conv per output phase
+// 16 zero bytes in device memory: the "filter" of an output phase that no tap reaches.
+static __device__ __align__(16) unsigned int g_zero_words[4];
+
+// One axis of one output phase. Outputs o = a0 + stride*t (t < T) receive x[i] * w[r] for i*stride - pad + r = o,
+// i.e. taps r = a + stride*j (j < taps) with a = (a0 + pad) % stride, from i = t + q0 - j, q0 = (a0 + pad) / stride.
+// With the taps reversed (j' = taps-1-j) that is a stride-1 correlation: i = t - pad_lo + j', pad_lo = taps-1-q0.
+// A negative pad_lo / pad_hi crops input rows instead (x_off rows from the front, extent `in` kept).
+struct PhaseAxis {
+  long long a0 = 0, T = 0, a = 0, taps = 0, x_off = 0, in = 0, pad_lo = 0, pad_hi = 0;
+  bool empty = false;   // no tap or no input row reaches this phase: its outputs are epilogue(0)
+};
+
+PhaseAxis phase_axis(long long in_extent, long long out_extent, long long filt, long long stride, long long pad,
+                     long long a0) {
+  PhaseAxis ax;
+  ax.a0 = a0;
+  ax.T = a0 < out_extent ? (out_extent - a0 + stride - 1) / stride : 0;
+  ax.a = (a0 + pad) % stride;
+  const long long q0 = (a0 + pad) / stride;
+  ax.taps = ax.a < filt ? (filt - ax.a + stride - 1) / stride : 0;
+  ax.in = in_extent;
+  ax.pad_lo = ax.taps - 1 - q0;
+  if (ax.pad_lo < 0) {
+    ax.x_off = -ax.pad_lo;
+    ax.in -= ax.x_off;
+    ax.pad_lo = 0;
+  }
+  ax.pad_hi = ax.T - ax.in - ax.pad_lo + (ax.taps - 1);
+  if (ax.pad_hi < 0) {
+    ax.in += ax.pad_hi;
+    ax.pad_hi = 0;
+  }
+  ax.empty = ax.taps == 0 || ax.in <= 0;
+  return ax;
+}
+
+// Geometry of an axis of an empty phase: a single zero tap over as much of the input as the outputs need.
+void make_empty_axis(PhaseAxis& ax, long long in_extent) {
+  ax.taps = 1;
+  ax.x_off = 0;
+  ax.in = std::min(in_extent, ax.T);
+  ax.pad_lo = 0;
+  ax.pad_hi = ax.T - ax.in;
+}
+
+// x, w, out, residual: device views in the conv's logical index order (x [N,C,H,W], w [K,C,R,S], out [N,K,Ho,Wo]).
+void conv_transpose_phases(int dev, const View4& x, const View4& w, const View4* bias, const View4* res,
+                           const View4& out, const TraceaConvTranspose2dParams& tp, const Epilogue& epi) {
+  const int es = elem_size(x.dtype);
+  const long long H = x.shape[2], W = x.shape[3], R = w.shape[2], S = w.shape[3];
+  const long long Ho = out.shape[2], Wo = out.shape[3];
+  const long long sh = tp.stride_h, sw = tp.stride_w;
+  void* zero_ptr = nullptr;
+  for (long long ah = 0; ah < sh; ++ah) {
+    for (long long aw = 0; aw < sw; ++aw) {
+      PhaseAxis ph = phase_axis(H, Ho, R, sh, tp.padding_h, ah);
+      PhaseAxis pw = phase_axis(W, Wo, S, sw, tp.padding_w, aw);
+      if (ph.T == 0 || pw.T == 0) continue;
+      const bool empty = ph.empty || pw.empty;
+      if (empty) {
+        make_empty_axis(ph, H);
+        make_empty_axis(pw, W);
+      }
+      View4 xp = x, wp = w, op = out, rp;
+      xp.ptr = static_cast<char*>(x.ptr) + (ph.x_off * x.stride[2] + pw.x_off * x.stride[3]) * es;
+      xp.shape[2] = ph.in;
+      xp.shape[3] = pw.in;
+      wp.shape[2] = ph.taps;
+      wp.shape[3] = pw.taps;
+      if (empty) {
+        if (zero_ptr == nullptr) {
+          DeviceGuard guard(dev);
+          TB_CUDA(cudaGetSymbolAddress(&zero_ptr, g_zero_words));
+        }
+        wp.ptr = zero_ptr;
+        wp.stride[0] = wp.stride[1] = wp.stride[2] = wp.stride[3] = 0;
+      } else {
+        // reversed taps: tap j' of the phase filter is w[.., a + stride*(taps-1-j'), ..]
+        wp.ptr = static_cast<char*>(w.ptr) +
+                 ((ph.a + sh * (ph.taps - 1)) * w.stride[2] + (pw.a + sw * (pw.taps - 1)) * w.stride[3]) * es;
+        wp.stride[2] = -sh * w.stride[2];
+        wp.stride[3] = -sw * w.stride[3];
+      }
+      auto phase_of = [&](const View4& v) {
+        View4 o = v;
+        o.ptr = static_cast<char*>(v.ptr) + (ah * v.stride[2] + aw * v.stride[3]) * es;
+        o.shape[2] = ph.T;
+        o.shape[3] = pw.T;
+        o.stride[2] = sh * v.stride[2];
+        o.stride[3] = sw * v.stride[3];
+        return o;
+      };
+      op = phase_of(out);
+      if (res != nullptr) rp = phase_of(*res);
+      CoreParams cp;
+      cp.stride_h = cp.stride_w = 1;
+      cp.dilation_h = cp.dilation_w = 1;
+      cp.groups = 1;
+      cp.epilogue = tp.epilogue;
+      cp.stream = tp.stream;
+      cp.padding_h = static_cast<uint32_t>(ph.pad_lo);
+      cp.padding_w = static_cast<uint32_t>(pw.pad_lo);
+      cp.pad_h_hi = ph.pad_hi;
+      cp.pad_w_hi = pw.pad_hi;
+      conv2d_device(dev, xp, wp, bias, res != nullptr ? &rp : nullptr, op, cp, epi);
+    }
+  }
+}
+
+// [d0, d1, d2, d3] view in (n, h, w, c) index order -> the conv's logical (n, c, h, w) order.
+View4 nhwc_to_logical(const View4& v) {
+  View4 o = v;
+  o.shape[1] = v.shape[3]; o.shape[2] = v.shape[1]; o.shape[3] = v.shape[2];
+  o.stride[1] = v.stride[3]; o.stride[2] = v.stride[1]; o.stride[3] = v.stride[2];
+  return o;
+}
+
+void conv_transpose2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, const TraceaTensorView* bv,
+                              const TraceaTensorView* rv, TraceaTensorView* ov, const TraceaConvTranspose2dParams& tp) {
+  if (xv.ptr == nullptr || wv.ptr == nullptr || ov == nullptr || ov->ptr == nullptr)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "Null pointer in input tensors");
+  if (tp.groups != 1) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "Unsupported groups: %u", tp.groups);
+  if (tp.stride_h == 0 || tp.stride_w == 0) TB_FAIL(TRACEA_INVALID_PARAMS, "stride must be >= 1");
+  if (tp.stride_h > 16 || tp.stride_w > 16) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "stride > 16 is not supported");
+  if (tp.dilation_h != 1 || tp.dilation_w != 1)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "Unsupported dilation: (%u, %u)", tp.dilation_h, tp.dilation_w);
+  if (tp.output_padding_h >= tp.stride_h || tp.output_padding_w >= tp.stride_w)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "output_padding must be smaller than the stride");
+  const int es = elem_size(xv.dtype);
+  if (es == 0)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "Unsupported dtype %s (float32, float16, bfloat16 are supported)",
+            dtype_name(xv.dtype));
+  if (wv.dtype != xv.dtype)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "x is %s but w is %s", dtype_name(xv.dtype), dtype_name(wv.dtype));
+  if (ov->dtype != xv.dtype)
+    TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "x is %s but out is %s", dtype_name(xv.dtype), dtype_name(ov->dtype));
+
+  View4 x = nhwc_to_logical(load_view4(xv, "x"));
+  View4 w = nhwc_to_logical(load_view4(wv, "w"));
+  View4 out = nhwc_to_logical(load_view4(*ov, "out"));
+  canon_channels_last(x);
+  canon_channels_last(out);
+  const long long N = x.shape[0], C = x.shape[1], H = x.shape[2], W = x.shape[3];
+  const long long K = w.shape[0], R = w.shape[2], S = w.shape[3];
+  if (w.shape[1] != C)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "Channel mismatch: x has %lld channels, w has %lld", C, w.shape[1]);
+  if (K == 0) TB_FAIL(TRACEA_INVALID_PARAMS, "w: shape[0] = 0 is out of range");
+  const long long Ho = (H - 1) * tp.stride_h - 2LL * tp.padding_h + R + tp.output_padding_h;
+  const long long Wo = (W - 1) * tp.stride_w - 2LL * tp.padding_w + S + tp.output_padding_w;
+  if (Ho <= 0 || Wo <= 0)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "padding (%u, %u) leaves no output for a %lldx%lld input and a %lldx%lld filter",
+            tp.padding_h, tp.padding_w, H, W, R, S);
+  if (out.shape[0] != N || out.shape[1] != K || out.shape[2] != Ho || out.shape[3] != Wo)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "out shape [%lld,%lld,%lld,%lld] does not match expected [%lld,%lld,%lld,%lld]",
+            out.shape[0], out.shape[2], out.shape[3], out.shape[1], N, Ho, Wo, K);
+  const int dev = x.device;
+  if (w.device != dev || out.device != dev)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "x, w and out must live on the same device");
+
+  View4 bias4, res4;
+  const View4* bias = nullptr;
+  const View4* res = nullptr;
+  if (bv != nullptr) {
+    if (bv->ptr == nullptr) TB_FAIL(TRACEA_INVALID_PARAMS, "bias view has a NULL pointer");
+    if (bv->rank != 1 || bv->shape == nullptr || (long long)bv->shape[0] != K)
+      TB_FAIL(TRACEA_INVALID_PARAMS, "bias must be a rank-1 tensor of length %lld", K);
+    if (bv->stride != nullptr && bv->stride[0] != 1) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "bias must be contiguous");
+    if (bv->dtype != TRACEA_DTYPE_FLOAT32 && bv->dtype != xv.dtype)
+      TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "bias must be float32 or %s", dtype_name(xv.dtype));
+    if (bv->device_id != dev) TB_FAIL(TRACEA_INVALID_PARAMS, "bias must live on the same device as x");
+    bias4.ptr = bv->ptr;
+    bias4.dtype = bv->dtype;
+    bias4.device = bv->device_id;
+    bias4.shape[0] = K;
+    bias4.shape[1] = bias4.shape[2] = bias4.shape[3] = 1;
+    bias4.stride[0] = 1;
+    bias = &bias4;
+  }
+  if (rv != nullptr) {
+    if (rv->ptr == nullptr) TB_FAIL(TRACEA_INVALID_PARAMS, "residual view has a NULL pointer");
+    res4 = nhwc_to_logical(load_view4(*rv, "residual"));
+    canon_channels_last(res4);
+    if (res4.dtype != xv.dtype) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "residual must be %s", dtype_name(xv.dtype));
+    for (int i = 0; i < 4; ++i)
+      if (res4.shape[i] != out.shape[i]) TB_FAIL(TRACEA_INVALID_PARAMS, "residual shape must equal the out shape");
+    if (res4.device != dev) TB_FAIL(TRACEA_INVALID_PARAMS, "residual must live on the same device as x");
+    res = &res4;
+  }
+  const Epilogue epi = decode_epilogue(tp.epilogue, bias != nullptr, res != nullptr);
+  if (N == 0) return;
+
+  if (dev >= 0) {
+    conv_transpose_phases(dev, x, w, bias, res, out, tp, epi);
+    return;
+  }
+  // host memory: stage whole tensors through the current device, run the phases, copy back and wait
+  int cur = 0;
+  TB_CUDA(cudaGetDevice(&cur));
+  cudaStream_t stream = static_cast<cudaStream_t>(tp.stream);
+  std::lock_guard<std::mutex> host_lock(g_host_path_mutex);
+  const bool use_bias = bias != nullptr && epi.bias, use_res = res != nullptr && epi.residual;
+  Staged sx, sw, sb, sr, so;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState& st = device_state(cur);
+    stage_in(st, x, sx, stream, true);
+    stage_in(st, w, sw, stream, true);
+    if (use_bias) stage_in(st, *bias, sb, stream, true);
+    if (use_res) stage_in(st, *res, sr, stream, true);
+    stage_in(st, out, so, stream, span_elems(out) != num_elems(out));
+  }
+  conv_transpose_phases(cur, sx.view, sw.view, use_bias ? &sb.view : nullptr, use_res ? &sr.view : nullptr, so.view, tp,
+                        epi);
+  TB_CUDA(cudaMemcpyAsync(out.ptr, so.buf.ptr, static_cast<size_t>(span_elems(out)) * es, cudaMemcpyDeviceToHost,
+                          stream));
+  TB_CUDA(cudaStreamSynchronize(stream));
+  const uint32_t code = tracea_b200_device_status(cur);
+  if (code != 0u) TB_FAIL(TRACEA_CUDA_ERROR, "conv kernel gave up a bounded wait (code %u)", code);
+}
+
+// ------------------------------------------------------------------ weight prepacking
+long long padded_channels(long long c, int es) {
+  const long long v = 16 / es;
+  return (c + v - 1) / v * v;
+}
+
+void launch_weight_pack(const void* src, void* dst, int es, long long K, long long C, long long R, long long S,
+                        long long Cp, const long long stride[4], cudaStream_t stream) {
+  const long long total = K * R * S * Cp;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+  if (R == 1 && S == 1 && (Cp + 31) / 32 <= 65535) {
+    dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>((Cp + 31) / 32), 1u);
+    dim3 block(32, 8);
+    if (es == 2)
+      tb200::to_channels_last_kernel<uint16_t><<<grid, block, 0, stream>>>(
+          static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), (int)C, 1, (int)K, (int)Cp, 0LL, stride[1], 0LL,
+          stride[0]);
+    else
+      tb200::to_channels_last_kernel<uint32_t><<<grid, block, 0, stream>>>(
+          static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), (int)C, 1, (int)K, (int)Cp, 0LL, stride[1], 0LL,
+          stride[0]);
+  } else if (es == 2) {
+    tb200::pack_weights_krsc_kernel<uint16_t><<<blocks, threads, 0, stream>>>(
+        static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), total, (int)C, (int)R, (int)S, (int)S, (int)Cp,
+        stride[0], stride[1], stride[2], stride[3]);
+  } else {
+    tb200::pack_weights_krsc_kernel<uint32_t><<<blocks, threads, 0, stream>>>(
+        static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), total, (int)C, (int)R, (int)S, (int)S, (int)Cp,
+        stride[0], stride[1], stride[2], stride[3]);
+  }
+  TB_CUDA(cudaGetLastError());
+}
+
+void conv2d_prepack_checked(const TraceaTensorView& wv, void* dst, uint64_t dst_bytes, uint64_t* packed_shape,
+                            int64_t* packed_stride, void* stream) {
+  if (wv.ptr == nullptr || dst == nullptr || packed_shape == nullptr || packed_stride == nullptr)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "Null pointer in prepack arguments");
+  const int es = elem_size(wv.dtype);
+  if (es == 0) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "Unsupported dtype %s", dtype_name(wv.dtype));
+  const View4 w = load_view4(wv, "w");
+  if (w.shape[0] == 0) TB_FAIL(TRACEA_INVALID_PARAMS, "w: shape[0] = 0 is out of range");
+  if (w.device < 0) TB_FAIL(TRACEA_INVALID_PARAMS, "prepacking takes device tensors (device_id >= 0)");
+  if (!aligned16(dst)) TB_FAIL(TRACEA_INVALID_PARAMS, "dst must be 16-byte aligned");
+  const long long K = w.shape[0], C = w.shape[1], R = w.shape[2], S = w.shape[3];
+  const long long Cp = padded_channels(C, es);
+  const unsigned long long need = (unsigned long long)(K * R * S * Cp) * es;
+  if (dst_bytes < need) TB_FAIL(TRACEA_INVALID_PARAMS, "dst holds %llu bytes, the packed weights need %llu",
+                                (unsigned long long)dst_bytes, need);
+  DeviceGuard guard(w.device);
+  launch_weight_pack(w.ptr, dst, es, K, C, R, S, Cp, w.stride, static_cast<cudaStream_t>(stream));
+  packed_shape[0] = (uint64_t)K; packed_shape[1] = (uint64_t)Cp; packed_shape[2] = (uint64_t)R; packed_shape[3] = (uint64_t)S;
+  packed_stride[0] = R * S * Cp; packed_stride[1] = 1; packed_stride[2] = S * Cp; packed_stride[3] = Cp;
+}
+
+void gemm_prepack_b_checked(const TraceaTensorView& bv, void* dst, uint64_t dst_bytes, int64_t* packed_stride,
+                            void* stream) {
+  if (bv.ptr == nullptr || dst == nullptr || packed_stride == nullptr)
+    TB_FAIL(TRACEA_INVALID_PARAMS, "Null pointer in prepack arguments");
+  const int es = elem_size(bv.dtype);
+  if (es == 0) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "Unsupported dtype %s", dtype_name(bv.dtype));
+  const Rank2 b = load_rank2(bv, "b");
+  if (b.shape[0] == 0 || b.shape[1] == 0) TB_FAIL(TRACEA_INVALID_PARAMS, "b must not be empty");
+  if (bv.device_id < 0) TB_FAIL(TRACEA_INVALID_PARAMS, "prepacking takes device tensors (device_id >= 0)");
+  if (!aligned16(dst)) TB_FAIL(TRACEA_INVALID_PARAMS, "dst must be 16-byte aligned");
+  const long long K = b.shape[0], N = b.shape[1];
+  const unsigned long long need = (unsigned long long)(K * N) * es;
+  if (dst_bytes < need) TB_FAIL(TRACEA_INVALID_PARAMS, "dst holds %llu bytes, the packed matrix needs %llu",
+                                (unsigned long long)dst_bytes, need);
+  DeviceGuard guard(bv.device_id);
+  const long long stride[4] = {b.stride[1], b.stride[0], 0, 0};   // filter bank [N, K, 1, 1]
+  launch_weight_pack(bv.ptr, dst, es, N, K, 1, 1, K, stride, static_cast<cudaStream_t>(stream));
+  packed_stride[0] = 1;
+  packed_stride[1] = K;
+}
+
 template <typename F>
 TraceaStatus guarded(const char* what, F&& f) {
   // mirrors the catch_unwind wrapper of tracea-ffi/src/lib.rs:130-141: nothing escapes the C boundary
@@ -1043,6 +1456,40 @@ TraceaStatus tracea_conv2d_noalloc(TraceaTensorView x, TraceaTensorView w, const
                                    const TraceaTensorView* residual, TraceaTensorView* out,
                                    TraceaConv2dParams params) {
   return guarded("tracea_conv2d_noalloc", [&] { conv2d_checked(x, w, b, residual, out, params, true); });
+}
+
+TraceaStatus tracea_gemm(TraceaTensorView a, TraceaTensorView b, const TraceaTensorView* bias,
+                         const TraceaTensorView* residual, TraceaTensorView* c, TraceaGemmParams params) {
+  return guarded("tracea_gemm", [&] { gemm_checked(a, b, bias, residual, c, params); });
+}
+
+TraceaStatus tracea_conv_transpose2d(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView* b,
+                                     const TraceaTensorView* residual, TraceaTensorView* out,
+                                     TraceaConvTranspose2dParams params) {
+  return guarded("tracea_conv_transpose2d", [&] { conv_transpose2d_checked(x, w, b, residual, out, params); });
+}
+
+uint64_t tracea_conv2d_prepack_bytes(TraceaTensorView w) {
+  const int es = elem_size(w.dtype);
+  if (es == 0 || w.rank != 4 || w.shape == nullptr) return 0;
+  return w.shape[0] * w.shape[2] * w.shape[3] * static_cast<uint64_t>(padded_channels((long long)w.shape[1], es)) * es;
+}
+
+TraceaStatus tracea_conv2d_prepack(TraceaTensorView w, void* dst, uint64_t dst_bytes, uint64_t packed_shape[4],
+                                   int64_t packed_stride[4], void* stream) {
+  return guarded("tracea_conv2d_prepack",
+                 [&] { conv2d_prepack_checked(w, dst, dst_bytes, packed_shape, packed_stride, stream); });
+}
+
+uint64_t tracea_gemm_prepack_b_bytes(TraceaTensorView b) {
+  const int es = elem_size(b.dtype);
+  if (es == 0 || b.rank != 2 || b.shape == nullptr) return 0;
+  return b.shape[0] * b.shape[1] * es;
+}
+
+TraceaStatus tracea_gemm_prepack_b(TraceaTensorView b, void* dst, uint64_t dst_bytes, int64_t packed_stride[2],
+                                   void* stream) {
+  return guarded("tracea_gemm_prepack_b", [&] { gemm_prepack_b_checked(b, dst, dst_bytes, packed_stride, stream); });
 }
 
 int32_t tracea_get_last_error(uint8_t* buf, size_t len) {

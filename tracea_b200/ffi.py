@@ -25,6 +25,8 @@ EXPORTED_SYMBOLS = (
     "tracea_conv2d", "tracea_conv2d_v0", "tracea_conv2d_noalloc", "tracea_get_last_error", "tracea_clear_error",
     "tracea_version_major", "tracea_version_minor", "tracea_version_patch", "tracea_init",
     "tracea_shutdown", "tracea_b200_device_status",
+    "tracea_gemm", "tracea_conv_transpose2d", "tracea_conv2d_prepack_bytes", "tracea_conv2d_prepack",
+    "tracea_gemm_prepack_b_bytes", "tracea_gemm_prepack_b",
 )
 
 
@@ -60,11 +62,27 @@ class Conv2dParamsV0(ctypes.Structure):
     ]
 
 
+class GemmParams(ctypes.Structure):
+    _fields_ = [("epilogue", ctypes.c_int), ("stream", ctypes.c_void_p)]
+
+
+class ConvTranspose2dParams(ctypes.Structure):
+    _fields_ = [
+        ("stride_h", ctypes.c_uint32), ("stride_w", ctypes.c_uint32),
+        ("padding_h", ctypes.c_uint32), ("padding_w", ctypes.c_uint32),
+        ("output_padding_h", ctypes.c_uint32), ("output_padding_w", ctypes.c_uint32),
+        ("dilation_h", ctypes.c_uint32), ("dilation_w", ctypes.c_uint32),
+        ("groups", ctypes.c_uint32),
+        ("epilogue", ctypes.c_int),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
 class TraceaError(RuntimeError):
     """A non-zero TraceaStatus, carrying the library's last-error text."""
 
-    def __init__(self, status, message):
-        super().__init__("tracea_conv2d failed: %s (%s)" % (message, STATUS_NAMES.get(status, status)))
+    def __init__(self, status, message, entry="tracea_conv2d"):
+        super().__init__("%s failed: %s (%s)" % (entry, message, STATUS_NAMES.get(status, status)))
         self.status = status
         self.message = message
 
@@ -103,6 +121,21 @@ def load():
     lib.tracea_shutdown.restype = None
     lib.tracea_b200_device_status.argtypes = [ctypes.c_int32]
     lib.tracea_b200_device_status.restype = ctypes.c_uint32
+    pv = ctypes.POINTER(TensorView)
+    lib.tracea_gemm.argtypes = [TensorView, TensorView, pv, pv, pv, GemmParams]
+    lib.tracea_gemm.restype = ctypes.c_int
+    lib.tracea_conv_transpose2d.argtypes = [TensorView, TensorView, pv, pv, pv, ConvTranspose2dParams]
+    lib.tracea_conv_transpose2d.restype = ctypes.c_int
+    lib.tracea_conv2d_prepack_bytes.argtypes = [TensorView]
+    lib.tracea_conv2d_prepack_bytes.restype = ctypes.c_uint64
+    lib.tracea_conv2d_prepack.argtypes = [TensorView, ctypes.c_void_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_uint64),
+                                          ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p]
+    lib.tracea_conv2d_prepack.restype = ctypes.c_int
+    lib.tracea_gemm_prepack_b_bytes.argtypes = [TensorView]
+    lib.tracea_gemm_prepack_b_bytes.restype = ctypes.c_uint64
+    lib.tracea_gemm_prepack_b.argtypes = [TensorView, ctypes.c_void_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_int64),
+                                          ctypes.c_void_p]
+    lib.tracea_gemm_prepack_b.restype = ctypes.c_int
     _lib = lib
     return lib
 
@@ -137,4 +170,28 @@ def conv2d_raw(x, w, bias, residual, out, stride=(1, 1), padding=(0, 0), dilatio
                            ctypes.byref(out.c) if out is not None else None, p)
     if check and st != SUCCESS:
         raise TraceaError(st, last_error())
+    return st
+
+
+def _opt(view):
+    return ctypes.byref(view.c) if view is not None else None
+
+
+def gemm_raw(a, b, bias, residual, c, epilogue=EPILOGUE_IDENTITY, stream=0, check=True):
+    """Call tracea_gemm with View objects (rank 2; bias rank 1)."""
+    st = load().tracea_gemm(a.c, b.c, _opt(bias), _opt(residual), _opt(c),
+                            GemmParams(int(epilogue), ctypes.c_void_p(stream)))
+    if check and st != SUCCESS:
+        raise TraceaError(st, last_error(), "tracea_gemm")
+    return st
+
+
+def conv_transpose2d_raw(x, w, bias, residual, out, stride=(1, 1), padding=(0, 0), output_padding=(0, 0),
+                         dilation=(1, 1), groups=1, epilogue=EPILOGUE_IDENTITY, stream=0, check=True):
+    """Call tracea_conv_transpose2d with View objects (x [N,H,W,C], w [K,R,S,C], out [N,Ho,Wo,K])."""
+    p = ConvTranspose2dParams(stride[0], stride[1], padding[0], padding[1], output_padding[0], output_padding[1],
+                              dilation[0], dilation[1], groups, int(epilogue), ctypes.c_void_p(stream))
+    st = load().tracea_conv_transpose2d(x.c, w.c, _opt(bias), _opt(residual), _opt(out), p)
+    if check and st != SUCCESS:
+        raise TraceaError(st, last_error(), "tracea_conv_transpose2d")
     return st

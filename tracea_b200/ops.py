@@ -11,6 +11,8 @@ Mirrors (paths relative to the reference project's root):
 torch is used for device memory and streams only. Every call goes through ``tracea_conv2d`` in
 libtracea_b200.so; nothing here computes a convolution itself.
 """
+import ctypes
+
 import torch
 
 from . import ffi
@@ -140,6 +142,73 @@ def conv2d(x, w, bias=None, residual=None, epilogue=None, stride=1, padding=0, d
     Context().conv2d(x, w, o, n_batch, c, h, w_in, k, r, s, stride=stride, pad=padding, dilation=dilation,
                      epilogue=epilogue, bias=bias, residual=residual)
     return o
+
+
+def gemm(x, w, bias=None, epilogue=None, residual=None):
+    """tracea.ops.gemm (tracea-python/python/tracea/ops.py:12-35): x (M, K) @ w (K, N) -> (M, N) with the conv
+    epilogue. Any strides; a ``w`` whose memory is [N][K] (``weight.t()`` of a Linear layer, or the result of
+    ``prepack_gemm_b``) is read in place, a row-major one is transposed into scratch on every call."""
+    if x.ndim != 2 or w.ndim != 2:
+        raise ValueError("Expected 2D tensors: x (M, K), w (K, N)")
+    if x.shape[1] != w.shape[0]:
+        raise ValueError(f"Inner dimension mismatch: x({x.shape[1]}) vs w({w.shape[0]})")
+    kind = parse_epilogue(epilogue, bias, residual)
+    out = torch.empty((x.shape[0], w.shape[1]), dtype=x.dtype, device=x.device)
+    ffi.gemm_raw(_view(x), _view(w), _view(bias) if bias is not None else None,
+                 _view(residual) if residual is not None else None, _view(out), kind, _stream_of(x))
+    return out
+
+
+def conv_transpose2d(x, w, bias=None, residual=None, epilogue=None, stride=1, padding=0, output_padding=0,
+                     dilation=1):
+    """tracea.ops.conv_transpose2d (tracea-python/python/tracea/ops.py:72-88): x (N, H, W, C), w (K, R, S, C),
+    optional bias (K) and residual (N, Ho, Wo, K); returns (N, Ho, Wo, K) with
+    Ho = (H-1)*stride - 2*padding + R + output_padding."""
+    if x.ndim != 4 or w.ndim != 4:
+        raise ValueError("Expected NHWC input and KRSC weight")
+    n_batch, h, w_in, c = x.shape
+    k, r, s, c_w = w.shape
+    if c != c_w:
+        raise ValueError(f"Channel mismatch: x({c}) vs w({c_w})")
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    oh, ow = _pair(output_padding)
+    h_out = (h - 1) * sh - 2 * ph + r + oh
+    w_out = (w_in - 1) * sw - 2 * pw + s + ow
+    kind = parse_epilogue(epilogue, bias, residual)
+    o = torch.empty((n_batch, h_out, w_out, k), dtype=x.dtype, device=x.device)
+    ffi.conv_transpose2d_raw(_view(x), _view(w), _view(bias) if bias is not None else None,
+                             _view(residual) if residual is not None else None, _view(o), (sh, sw), (ph, pw),
+                             (oh, ow), _pair(dilation), 1, kind, _stream_of(x))
+    return o
+
+
+def prepack_conv2d_weight(w):
+    """OIHW-shaped weights of any strides -> a tensor of the same logical shape (channels rounded up to 16 bytes)
+    whose memory is the dense [K][R][S][C] layout the kernel reads in place (tracea_conv2d_prepack)."""
+    lib = ffi.load()
+    v = _view(w)
+    nbytes = lib.tracea_conv2d_prepack_bytes(v.c)
+    shape = (ctypes.c_uint64 * 4)()
+    stride = (ctypes.c_int64 * 4)()
+    buf = torch.empty(nbytes // w.element_size(), dtype=w.dtype, device=w.device)
+    st = lib.tracea_conv2d_prepack(v.c, buf.data_ptr(), nbytes, shape, stride, _stream_of(w))
+    if st != ffi.SUCCESS:
+        raise ffi.TraceaError(st, ffi.last_error(), "tracea_conv2d_prepack")
+    return torch.as_strided(buf, tuple(int(d) for d in shape), tuple(int(d) for d in stride))
+
+
+def prepack_gemm_b(b):
+    """(K, N) matrix of any strides -> a (K, N) tensor whose memory is [N][K] (tracea_gemm_prepack_b)."""
+    lib = ffi.load()
+    v = _view(b)
+    nbytes = lib.tracea_gemm_prepack_b_bytes(v.c)
+    stride = (ctypes.c_int64 * 2)()
+    buf = torch.empty(nbytes // b.element_size(), dtype=b.dtype, device=b.device)
+    st = lib.tracea_gemm_prepack_b(v.c, buf.data_ptr(), nbytes, stride, _stream_of(b))
+    if st != ffi.SUCCESS:
+        raise ffi.TraceaError(st, ffi.last_error(), "tracea_gemm_prepack_b")
+    return torch.as_strided(buf, tuple(b.shape), (int(stride[0]), int(stride[1])))
 
 
 class Context:
