@@ -227,6 +227,7 @@ def run_ours(args):
     # ---- timed region: K steps, device-timed; an event between launches gives per-layer durations
     nl = len(specs)
     events = [torch.cuda.Event(enable_timing=True) for _ in range(steps * nl + 1)]
+    launches_before = lib.tracea_b200_launch_count()
     with ClockSampler(local_rank) as clocks:
         events[0].record(stream)
         for i in range(steps):
@@ -235,6 +236,7 @@ def run_ours(args):
                 st.launch_one(j)
                 events[i * nl + j + 1].record(stream)
         barrier()
+    launches = lib.tracea_b200_launch_count() - launches_before   # counted by the library itself, this rank
     status = lib.tracea_b200_device_status(local_rank)
     if status != 0:
         raise RuntimeError("a conv kernel gave up a bounded wait (device status %d)" % status)
@@ -358,7 +360,7 @@ def run_ours(args):
             "layers": [{"name": s.name, "ms": layer_ms[j], "tflops": resnet50.conv_flops(s, n) / layer_ms[j] / 1e9,
                         "algorithmic_gbs": resnet50.conv_bytes(s, n) / layer_ms[j] / 1e6}
                        for j, s in enumerate(specs)],
-            "roofline": {"kernel": "conv2d_igemm_sm100_kernel<bf16,256> on the 3x3 256->256 conv", "bound": "tensor",
+            "roofline": {"kernel": "conv2d_igemm_sm100_kernel<bf16,256,pair> on the 3x3 256->256 conv", "bound": "tensor",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                          "peak_source": "%s %s cuBLAS bf16" % (peaks["source"], "sustained" if sustained else "burst"),
                          "traffic": CONV3X3_NCU_TRAFFIC_BYTES, "algorithmic_bytes": resnet50.conv_bytes(c2, n),
@@ -366,7 +368,8 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world,
                     "d2h_bytes_per_step": d2h * world, "steps": e2e_steps, "ms_per_step": e2e_median,
                     "ms_per_step_mean": e2e_mean, "stat": "median of the per-step times"},
-            "gpu_launches": steps * nl * world,
+            "gpu_launches": launches * world,
+            "gpu_launches_per_step": launches / steps,
             "clocks": clocks.summary(),
             "resnet50": extra,
         }

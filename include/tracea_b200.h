@@ -231,6 +231,11 @@ void tracea_shutdown(void);
  * has no counterpart: its kernels spin without limit. */
 uint32_t tracea_b200_device_status(int32_t device_id);
 
+/* Number of GPU kernels this library has launched in this process so far (conv kernels and layout adapters;
+ * a call may launch more than one: a layout adapter per staged operand, one conv launch per phase of a transposed
+ * convolution). Benchmarks read it before and after a timed region. No counterpart in the reference. */
+uint64_t tracea_b200_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -91,9 +91,10 @@ def test_conv_transpose_reads_the_reference_kernels_crsk_weight_memory():
     assert torch.equal(a, b)
 
 
-def test_conv_transpose_stride1_is_the_conv_with_flipped_taps_bit_exactly():
-    x = cc.normal((2, 10, 10, 32), 5, "ctf/x")
-    w = cc.normal((16, 3, 3, 32), 5, "ctf/w", 0.06)
+@pytest.mark.parametrize("C", [32, 64, 192])    # 64-byte k-chunks: phase filters are gathered; 128-byte: read in place
+def test_conv_transpose_stride1_is_the_conv_with_flipped_taps_bit_exactly(C):
+    x = cc.normal((2, 10, 10, C), 5, "ctf/x")
+    w = cc.normal((16, 3, 3, C), 5, "ctf/w", 0.06)
     tx, tw = dev(x, "bf16"), dev(w, "bf16")
     a = ops.conv_transpose2d(tx, tw, stride=1, padding=1)
     b = ops.conv2d(tx, torch.flip(tw, (1, 2)).contiguous(), stride=1, padding=1)   # pad' = R - 1 - pad = 1
@@ -165,6 +166,18 @@ def test_gemm_operand_layouts_give_identical_results(layout):
     else:
         other = ops.gemm(ta, tb, tbias, "bias+relu")
     assert torch.equal(other, base)
+
+
+def test_gemm_reads_a_padded_pitch_b_in_place():
+    M, K, N = 300, 128, 72
+    a = dev(cc.normal((M, K), 8, "gp/a"), "bf16")
+    storage = torch.zeros((N, K + 64), dtype=torch.bfloat16, device="cuda")       # [N][K] rows with a 64-element gap
+    storage[:, :K] = dev(cc.normal((N, K), 8, "gp/b", K ** -0.5), "bf16")
+    b = storage[:, :K].t()                                                          # (K, N), strides (1, K + 64)
+    before = ffi.load().tracea_b200_launch_count()
+    got = ops.gemm(a, b)
+    assert ffi.load().tracea_b200_launch_count() - before == 1                      # no transpose kernel ran
+    assert torch.equal(got, ops.gemm(a, b.contiguous()))
 
 
 def test_gemm_fc_head_shape_and_host_tensors():

@@ -48,7 +48,8 @@ enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3 };
 
 struct ConvKernelArgs {
   // problem
-  int M;            // N * Ho * Wo
+  int M;            // one past the last output pixel (row of the implicit GEMM) this launch owns
+  int m_begin;      // first output pixel this launch owns: tile t covers rows m_begin + t * rows-per-tile ...
   int K_out;        // output channels
   int Ho, Wo;
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
@@ -60,6 +61,11 @@ struct ConvKernelArgs {
   int total_chunks;       // R * S * chunks_per_tap
   int C;                  // input channels (c coordinate >= C reads zeros)
   int a_tiled;            // 1: A is a plain [M][C] matrix (1x1, stride 1, no padding) read by tiled TMA
+  // B's column (element index inside one output channel's weight row) of tap (r, s), channel c is
+  // b_k0 + r * (row stride) + s * (tap stride) + c. The loader walks it incrementally: +chunk_elems per k-step,
+  // +b_jump_s at every tap boundary, +b_jump_r more at every filter-row boundary. Dense [R][S][C] rows: all 0.
+  // Non-zero jumps are only used with 128-byte chunks (one chunk per stage).
+  int b_k0, b_jump_s, b_jump_r;
   int prefetch_dist;      // > 0: the producer L2-prefetches A this many k-steps ahead of its loads
   // tiling / pipeline
   int num_m_tiles, num_n_tiles;
@@ -304,6 +310,48 @@ __device__ __noinline__ void epilogue_block_generic(const ConvKernelArgs& args, 
 // kRows2 (single CTA, narrow outputs): the CTA owns a 256 x BN tile as two 128-row blocks with one accumulator
 // each; a stage carries both A blocks and one B, i.e. eight MMAs per barrier probe instead of four, and the two
 // epilogue groups drain the two halves of the same tile instead of alternate tiles.
+// Staging box (32 pixel rows x 128 bytes, SWIZZLE_128B layout: 16-byte chunk c of row r at r*128 + ((c ^ (r & 7)) << 4))
+// <-> global memory, moved by the warp itself for outputs the TMA unit cannot address as one matrix. Lane l handles
+// chunk l & 7 of rows (l >> 3) + 4 i, so each instruction covers four whole 128-byte rows. `row_base` points at the
+// first element of the group's columns in pixel 0's row; `row_off` is this lane's own pixel offset (in elements),
+// `row_ok` whether its pixel exists; `cols_left` = K_out - first column of the group. Out of line on purpose: the
+// TMA path's register allocation must not pay for this one.
+template <typename OutT>
+__device__ __noinline__ void coop_store_box(uint32_t stg, OutT* row_base, long long row_off, bool row_ok, int cols_left,
+                                            int lane) {
+  constexpr int kVec = 16 / sizeof(OutT);
+  __syncwarp();   // every lane's row is in the box
+  const uint32_t ok_rows = __ballot_sync(0xffffffffu, row_ok);
+  const uint32_t chunk = static_cast<uint32_t>(lane) & 7u;
+  const bool chunk_ok = static_cast<int>(chunk) * kVec < cols_left;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    const long long off = __shfl_sync(0xffffffffu, row_off, r);
+    const uint4 v = ptx::ld_shared_v4(stg + static_cast<uint32_t>(r) * 128u + ((chunk ^ (static_cast<uint32_t>(r) & 7u)) << 4));
+    if (chunk_ok && ((ok_rows >> r) & 1u)) *(reinterpret_cast<uint4*>(row_base + off) + chunk) = v;
+  }
+  __syncwarp();   // the box may be rewritten once every lane has read it out
+}
+
+template <typename OutT>
+__device__ __noinline__ void coop_load_box(uint32_t stg, const OutT* row_base, long long row_off, bool row_ok,
+                                           int cols_left, int lane) {
+  constexpr int kVec = 16 / sizeof(OutT);
+  const uint32_t ok_rows = __ballot_sync(0xffffffffu, row_ok);
+  const uint32_t chunk = static_cast<uint32_t>(lane) & 7u;
+  const bool chunk_ok = static_cast<int>(chunk) * kVec < cols_left;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    const long long off = __shfl_sync(0xffffffffu, row_off, r);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (chunk_ok && ((ok_rows >> r) & 1u)) v = __ldg(reinterpret_cast<const uint4*>(row_base + off) + chunk);
+    ptx::st_shared_v4(stg + static_cast<uint32_t>(r) * 128u + ((chunk ^ (static_cast<uint32_t>(r) & 7u)) << 4), v);
+  }
+  __syncwarp();   // rows were written by other lanes than the ones that read them next
+}
+
 template <typename OutT, int BN, bool kPair, bool kRows2>
 __global__ void __launch_bounds__(kNumThreads, 1)
 conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
@@ -422,7 +470,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         uint32_t off_w, off_h;
       } pf = {};
       auto pf_begin_tile = [&]() {
-        const int pm0 = pf.m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
+        const int pm0 = args.m_begin + pf.m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
         const int pt = pm0 / args.Wo;
         pf.w_start = (pm0 % args.Wo) * args.stride_w - args.pad_w;
         pf.h_start = (pt % args.Ho) * args.stride_h - args.pad_h;
@@ -453,7 +501,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         for (int i = 0; i < args.prefetch_dist; ++i) pf_step();
       }
       for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
-        const int m0 = m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;   // this CTA's 128 pixels
+        const int m0 = args.m_begin + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;   // this CTA's 128 pixels
         const int q0 = m0 % args.Wo;
         const int t = m0 / args.Wo;
         const int p0 = t % args.Ho;
@@ -471,7 +519,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         if (one_chunk) {
           // common case: one 128-byte chunk per stage = 64 (16-bit) or 32 (fp32) channels of one tap
-          int c_coord = 0, k_coord = 0, tap_s = 0;
+          int c_coord = 0, k_coord = args.b_k0, tap_s = 0;
           uint32_t off_w = 0, off_h = 0;
           for (int it = 0; it < k_iters; ++it) {
             TB200_PROF_T(tw);
@@ -507,7 +555,8 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             if (c_coord == args.C) {
               c_coord = 0;
               off_w += args.dil_w;
-              if (++tap_s == args.S) { tap_s = 0; off_w = 0; off_h += args.dil_h; }
+              k_coord += args.b_jump_s;
+              if (++tap_s == args.S) { tap_s = 0; off_w = 0; off_h += args.dil_h; k_coord += args.b_jump_r; }
             }
             ++issued;
             stage_addr = nstage; full_addr = nfull; empty_addr = nempty; phase = nphase;
@@ -721,6 +770,11 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     TB200_PROF_T(prof_t0);
     int m_tile = etile0 / args.num_n_tiles - estep_m, n_tile = etile0 % args.num_n_tiles - estep_n;
     const bool need_coords = !args.out_tma || (res != nullptr && !res_tma);
+    // Channel-contiguous outputs whose pixels are not one dense [M][pitch] matrix (a strided view, one phase of a
+    // transposed convolution) take the same staging boxes as the TMA path, but the warp moves them itself:
+    // 8 lanes per pixel, 16 bytes each, so every store / residual load instruction covers 4 whole 128-byte rows.
+    const bool coop = !args.out_tma && args.out_vec != 0 && (res == nullptr || args.res_vec != 0);
+    const bool res_staged = res_tma || (coop && res != nullptr);
     for (int tile = etile0; tile < num_tiles && ok; tile += estride, local_tile += (kRows2 ? 1 : 2)) {
       n_tile += estep_n; m_tile += estep_m;
       if (n_tile >= args.num_n_tiles) { n_tile -= args.num_n_tiles; ++m_tile; }
@@ -729,7 +783,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
       const int n_base = n_tile * BN;
       const int row_block = kPair ? static_cast<int>(cta_rank) : (kRows2 ? egroup : 0);   // which 128 rows of the tile
-      const int m_row0 = m_tile * kTileM + row_block * kBlockM + quarter * 32;
+      const int m_row0 = args.m_begin + m_tile * kTileM + row_block * kBlockM + quarter * 32;
 
       // this warp's fp32 copy of the tile's bias (zeros when there is none / past K_out); the values
       // were fetched into registers during the previous tile, and the next tile's are fetched now
@@ -746,7 +800,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         fetch_bias(nn);
       }
 
-      const int m = m_tile * kTileM + row_block * kBlockM + row;
+      const int m = args.m_begin + m_tile * kTileM + row_block * kBlockM + row;
       const bool row_ok = m < args.M;
       long long out_off = 0, res_off = 0;
       if (need_coords) {   // only the per-lane store / load paths need (n, ho, wo); the TMA paths do not
@@ -830,6 +884,8 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (lane == 0) bulk_wait_group_read<1>();   // this box's previous store (two groups ago) has been read out
           __syncwarp();
           TB200_PROF_ADD(prof_wstore, ts);
+        } else if (coop && res != nullptr) {
+          coop_load_box<OutT>(stg, res + n0, res_off, row_ok, args.K_out - n0, lane);
         }
 
         TB200_PROF_T(tm);
@@ -845,7 +901,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             add2(f[j4 * 4 + 0], f[j4 * 4 + 1], b4.x, b4.y);
             add2(f[j4 * 4 + 2], f[j4 * 4 + 3], b4.z, b4.w);
           }
-          if (!args.out_tma) {
+          if (!args.out_tma && !coop) {
             float fg[32];   // a copy the out-of-line path may keep in local memory; f stays in registers
 #pragma unroll
             for (int j = 0; j < 32; ++j) fg[j] = f[j];
@@ -857,7 +913,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           // TMA output; a residual, if any, sits in this lane's row of the staging box (the host
           // guarantees a residual is TMA-loaded whenever the output is TMA-stored)
           uint4 rchunks[kChunksPerLd];
-          if (res_tma) {
+          if (res_staged) {
 #pragma unroll
             for (int c = 0; c < kChunksPerLd; ++c) {
               const uint32_t cc = static_cast<uint32_t>(h * kChunksPerLd + c);
@@ -865,9 +921,9 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             }
           }
           if (args.act == kActRelu) {
-            finish32<OutT, true>(f, rchunks, res_tma, packed + h * kChunksPerLd);
+            finish32<OutT, true>(f, rchunks, res_staged, packed + h * kChunksPerLd);
           } else {
-            if (res_tma) {
+            if (res_staged) {
 #pragma unroll
               for (int c = 0; c < kChunksPerLd; ++c) add16<OutT>(f + c * kVec, rchunks[c]);
             }
@@ -888,6 +944,12 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             tma_store_2d(&tmap_out, stg, n0, m_row0);
             bulk_commit_group();
           }
+          box ^= 1u;
+        } else if (coop) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            st_shared_v4(stg + lane_row_off + ((static_cast<uint32_t>(c) ^ lane_xor) << 4), packed[c]);
+          coop_store_box<OutT>(stg, out + n0, out_off, row_ok, args.K_out - n0, lane);
           box ^= 1u;
         }
         TB200_PROF_ADD(prof_stage, tg);

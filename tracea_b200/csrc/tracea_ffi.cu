@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -85,6 +86,7 @@ constexpr int kMaxDevices = 64;
 std::mutex g_mutex;
 std::mutex g_host_path_mutex;   // one host-memory call at a time per process (it owns the copy streams)
 DeviceState g_dev[kMaxDevices];
+std::atomic<unsigned long long> g_kernel_launches{0};   // every kernel this library has launched (conv + layout adapters)
 EncodeTiledFn g_encode_tiled = nullptr;
 EncodeIm2colFn g_encode_im2col = nullptr;
 
@@ -330,6 +332,7 @@ void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, 
     kern<<<grid, tb200::kNumThreads, smem, stream>>>(tx, tw, to, tr, args);
   }
   TB_CUDA(cudaGetLastError());
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
 template <typename OutT>
@@ -373,6 +376,23 @@ CUtensorMapSwizzle tmap_swizzle(int chunk_bytes) {
 int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
   return (v != nullptr && *v != '\0') ? atoi(v) : dflt;
+}
+
+// Bring-up / test knobs, read from the environment once per process (a getenv per knob per call is a measurable
+// part of the ~6 us a call costs on the host). TRACEA_B200_HOST_CHUNKS is read per call and is not in here.
+struct Knobs {
+  int force_bn, force_stages, force_chunk, no_tma_store, no_tma_residual, tiled_a, force_staging, no_window, prefetch,
+      pair, rows2;
+};
+const Knobs& knobs() {
+  static const Knobs k = {
+      env_int("TRACEA_B200_FORCE_BN", 0),      env_int("TRACEA_B200_FORCE_STAGES", 0),
+      env_int("TRACEA_B200_FORCE_CHUNK", 0),   env_int("TRACEA_B200_NO_TMA_STORE", 0),
+      env_int("TRACEA_B200_NO_TMA_RESIDUAL", 0), env_int("TRACEA_B200_TILED_A", 0),
+      env_int("TRACEA_B200_FORCE_STAGING", 0), env_int("TRACEA_B200_NO_WINDOW", 0),
+      env_int("TRACEA_B200_PREFETCH", 0),      env_int("TRACEA_B200_PAIR", -1),
+      env_int("TRACEA_B200_ROWS2", -1)};
+  return k;
 }
 
 // ------------------------------------------------------------------ static scratch (no-alloc entry)
@@ -513,7 +533,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   // horizontal padding materialised; one filter row of a pixel is then 8 adjacent pixels = one 128-byte
   // k-chunk, fetched by a single im2col copy over an overlapping view (pixel pitch 16 B, "pixel" size 128 B).
   const bool window = Cp * es == 16 && S > 1 && S <= 8 && p.dilation_w == 1 && W + 2LL * p.padding_w < (1LL << 30) &&
-                      p.pad_w_hi == (long long)p.padding_w && env_int("TRACEA_B200_NO_WINDOW", 0) == 0;
+                      p.pad_w_hi == (long long)p.padding_w && knobs().no_window == 0;
   const long long Wpitch = W + 2LL * p.padding_w + 8;   // row pitch of the padded copy, in pixels
 
   // ---- activations: consume channels-last memory directly, otherwise transpose into scratch
@@ -536,12 +556,13 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
           static_cast<const uint32_t*>(x.ptr), static_cast<uint32_t*>(x_stage), (int)C, (int)H, (int)W, (int)Wpitch,
           (int)p.padding_w, pixels, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
     TB_CUDA(cudaGetLastError());
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
     x.ptr = x_stage;
     x.stride[0] = H * Wpitch * Cp;
     x.stride[1] = 1;
     x.stride[2] = Wpitch * Cp;
     x.stride[3] = Cp;
-  } else if (!x_direct || env_int("TRACEA_B200_FORCE_STAGING", 0)) {
+  } else if (!x_direct || knobs().force_staging) {
     void* x_stage = staging(x_scratch, static_cast<size_t>(N * H * W * Cp) * es, "the channels-last copy of x");
     dim3 grid(static_cast<unsigned>((H * W + 31) / 32), static_cast<unsigned>((Cp + 31) / 32),
               static_cast<unsigned>(N));
@@ -557,6 +578,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
           static_cast<const uint32_t*>(x.ptr), static_cast<uint32_t*>(x_stage), (int)C, (int)H,
           (int)W, (int)Cp, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
     TB_CUDA(cudaGetLastError());
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
     x.ptr = x_stage;
     x.stride[0] = H * W * Cp;
     x.stride[1] = 1;
@@ -564,11 +586,55 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     x.stride[3] = Cp;
   }
 
-  // ---- weights: consume dense [K][R][S][C] memory directly, otherwise repack into scratch
+  // ---- k-chunking: the widest power-of-two row (<= 128 B) that divides one pixel's channels
+  // In window mode the kernel sees a conv with one tap per filter row over "pixels" of 8 * Cp channels.
+  const long long Cg = window ? 8 * Cp : Cp;      // channel extent of the kernel's view
+  const long long Sg = window ? 1 : S;            // taps per filter row of the kernel's view
+  const long long row_bytes = Cg * es;
+  int chunk_bytes = 16;
+  for (int cb = 128; cb >= 16; cb >>= 1) {
+    if (row_bytes % cb == 0) {
+      chunk_bytes = cb;
+      break;
+    }
+  }
+  const int forced_chunk = knobs().force_chunk;
+  if (forced_chunk == 16 || forced_chunk == 32 || forced_chunk == 64 || forced_chunk == 128) {
+    if (row_bytes % forced_chunk == 0) chunk_bytes = forced_chunk;
+  }
+  const int chunk_elems = chunk_bytes / es;
+  const int chunks_per_tap = static_cast<int>(Cg / chunk_elems);
+  const long long total_chunks_ll = R * Sg * chunks_per_tap;
+  if (total_chunks_ll > 0x7fffffffLL / 128) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "R*S*C too large");
+
+  // ---- weights. Read in place when every output channel's taps are channel-contiguous and lie inside its own
+  // row of a [K][row] matrix: the dense [K][R][S][C] layout, and -- with 128-byte k-chunks, where the loader walks
+  // Kgemm one tap-slice at a time -- any tap order reachable by strides (reversed / subsampled taps: the phase
+  // filters of a transposed convolution). The loader then starts at column b_k0 and adds b_jump_s / b_jump_r to its
+  // column at every tap / filter-row boundary. Anything else is repacked into scratch.
   const void* w_ptr = w_in.ptr;
   Scratch w_scratch;
-  const bool w_direct = C == Cp && (w_in.stride[1] == 1) && w_in.stride[3] == C &&
-                        w_in.stride[2] == S * C && w_in.stride[0] == R * S * C && aligned16(w_in.ptr);
+  long long w_row_elems = R * S * C, w_pitch = R * S * C, b_k0 = 0, b_jump_s = 0, b_jump_r = 0;
+  const bool w_dense = C == Cp && (w_in.stride[1] == 1) && w_in.stride[3] == C &&
+                       w_in.stride[2] == S * C && w_in.stride[0] == R * S * C && aligned16(w_in.ptr);
+  bool w_direct = w_dense, w_remap = false;
+  if (!w_dense && !window && C == Cp && w_in.stride[1] == 1 && chunk_bytes == 128) {
+    const long long ss = S == 1 ? C : w_in.stride[3], sr = R == 1 ? S * ss : w_in.stride[2], sk = w_in.stride[0];
+    const long long lo = std::min(0LL, (R - 1) * sr) + std::min(0LL, (S - 1) * ss);
+    const long long hi = std::max(0LL, (R - 1) * sr) + std::max(0LL, (S - 1) * ss) + C;
+    const char* base = static_cast<const char*>(w_in.ptr) + lo * es;
+    const bool taps_apart = (ss >= C || ss <= -C) && (R == 1 || sr >= C || sr <= -C);
+    if (taps_apart && (K == 1 || sk >= hi - lo) && (sk * es) % 16 == 0 && (ss * es) % 16 == 0 && (sr * es) % 16 == 0 &&
+        aligned16(base) && hi - lo < (1LL << 31)) {
+      w_direct = w_remap = true;
+      w_ptr = base;
+      w_row_elems = hi - lo;
+      w_pitch = K == 1 ? hi - lo : sk;
+      b_k0 = -lo;
+      b_jump_s = ss - C;
+      b_jump_r = sr - S * ss;
+    }
+  }
   const long long Sd = window ? 8 : S;   // tap slots per filter row in the packed weights
   if (!w_direct || window) {
     const long long total = K * R * Sd * Cp;
@@ -597,61 +663,41 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
           static_cast<const uint32_t*>(w_in.ptr), static_cast<uint32_t*>(w_stage), total, (int)C,
           (int)R, (int)S, (int)Sd, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
     TB_CUDA(cudaGetLastError());
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
     w_ptr = w_stage;
   }
 
-  // ---- k-chunking: the widest power-of-two row (<= 128 B) that divides one pixel's channels
-  // In window mode the kernel sees a conv with one tap per filter row over "pixels" of 8 * Cp channels.
-  const long long Cg = window ? 8 * Cp : Cp;      // channel extent of the kernel's view
-  const long long Sg = window ? 1 : S;            // taps per filter row of the kernel's view
-  const long long row_bytes = Cg * es;
-  int chunk_bytes = 16;
-  for (int cb = 128; cb >= 16; cb >>= 1) {
-    if (row_bytes % cb == 0) {
-      chunk_bytes = cb;
-      break;
-    }
-  }
-  const int forced_chunk = env_int("TRACEA_B200_FORCE_CHUNK", 0);
-  if (forced_chunk == 16 || forced_chunk == 32 || forced_chunk == 64 || forced_chunk == 128) {
-    if (row_bytes % forced_chunk == 0) chunk_bytes = forced_chunk;
-  }
-  const int chunk_elems = chunk_bytes / es;
-  const int chunks_per_tap = static_cast<int>(Cg / chunk_elems);
-  const long long total_chunks_ll = R * Sg * chunks_per_tap;
-  if (total_chunks_ll > 0x7fffffffLL / 128) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "R*S*C too large");
   const long long Kgemm = R * Sg * Cg;
 
-  // ---- tiles
-  long long m_tiles = (M + tb200::kBlockM - 1) / tb200::kBlockM;
-  int bn = pick_bn(m_tiles, static_cast<int>(K), st.num_sms);
-  const int forced_bn = env_int("TRACEA_B200_FORCE_BN", 0);
+  // ---- tiling of the whole problem
+  const long long m_tiles_128 = (M + tb200::kBlockM - 1) / tb200::kBlockM;
+  int bn = pick_bn(m_tiles_128, static_cast<int>(K), st.num_sms);
+  const int forced_bn = knobs().force_bn;
   if (forced_bn == 64 || forced_bn == 128 || forced_bn == 256) bn = forced_bn;
   // CTA pairs (cta_group::2): a pair of SMs owns a 256 x bn tile and each CTA brings in only half of B's rows
   // Worth it when the main loop is long enough to dominate the tile (>= 8 k-steps); short-K, epilogue-bound
   // layers lose more from coupling two SMs' epilogues than they gain. TRACEA_B200_PAIR=0/1 forces the choice.
-  const int pair_env = env_int("TRACEA_B200_PAIR", -1);
+  const int pair_env = knobs().pair;
   const bool pair_ok = chunk_bytes == 128 && bn == 256 && st.num_sms >= 2;
   const bool pair = pair_ok && (pair_env == 1 || (pair_env != 0 && total_chunks_ll >= 8));
   // Two row blocks per CTA for narrow outputs (bn <= 128): twice the tensor work per barrier probe and per tile.
-  const int rows2_env = env_int("TRACEA_B200_ROWS2", -1);
-  const bool rows2 = !pair && chunk_bytes == 128 && bn <= 128 && rows2_env != 0 &&
-                     (rows2_env == 1 || (total_chunks_ll >= 7 && m_tiles >= 2LL * st.num_sms));
-  if (pair || rows2) m_tiles = (M + 2 * tb200::kBlockM - 1) / (2 * tb200::kBlockM);
+  const int rows2_env = knobs().rows2;
+  // A 256-row tile costs an SM about 1.6x what a 128-row tile costs it (measured; the narrow tile is bound by the
+  // shared-memory fill rate, which B's reuse across two row blocks relieves): taken when it shortens the launch,
+  // wave quantisation included.
   const long long n_tiles = (K + bn - 1) / bn;
-  if (m_tiles * n_tiles > 0x7fffffffLL) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "too many tiles");
-  int stages = pick_stages(bn, pair, rows2);
-  const int forced_stages = env_int("TRACEA_B200_FORCE_STAGES", 0);
-  if (forced_stages >= 2 && forced_stages <= stages) stages = forced_stages;
-  const int smem = tb200::conv_smem_bytes(bn, stages, pair, rows2);
+  const long long waves_128 = (m_tiles_128 * n_tiles + st.num_sms - 1) / st.num_sms;
+  const long long waves_256 = ((m_tiles_128 + 1) / 2 * n_tiles + st.num_sms - 1) / st.num_sms;
+  const bool rows2 = !pair && chunk_bytes == 128 && bn <= 128 && rows2_env != 0 &&
+                     (rows2_env == 1 || (total_chunks_ll >= 7 && 8 * waves_256 < 5 * waves_128));
 
-  // ---- tensor maps
-  CUtensorMap tmap_x, tmap_w, tmap_out, tmap_res;
+  // ---- tensor maps shared by every launch of this call
+  CUtensorMap tmap_x, tmap_out, tmap_res;
   memset(&tmap_out, 0, sizeof(tmap_out));
   memset(&tmap_res, 0, sizeof(tmap_res));
   // A 1x1 / stride-1 / unpadded conv over dense NHWC memory is a plain [M][C] x [C][K] GEMM; the
   // tiled map is kept as a cross-check of the im2col path (TRACEA_B200_TILED_A=1).
-  const bool a_tiled = !pair && !rows2 && !window && env_int("TRACEA_B200_TILED_A", 0) != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
+  const bool a_tiled = !pair && !rows2 && !window && knobs().tiled_a != 0 && R == 1 && S == 1 && p.stride_h == 1 &&
                        p.stride_w == 1 && p.padding_h == 0 && p.padding_w == 0 && p.pad_h_hi == 0 && p.pad_w_hi == 0 &&
                        x.stride[3] == Cp &&
                        x.stride[2] == W * Cp && x.stride[0] == H * W * Cp;
@@ -687,23 +733,10 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
               (int)r, Cg, W, H, N, chunk_bytes, lower[0], lower[1], upper[0], upper[1], p.stride_w,
               p.stride_h);
   }
-  {
-    const cuuint64_t gdim[2] = {(cuuint64_t)Kgemm, (cuuint64_t)K};
-    const cuuint64_t gstr[1] = {(cuuint64_t)(Kgemm * es)};
-    const cuuint32_t box[2] = {(cuuint32_t)chunk_elems, (cuuint32_t)(pair ? bn / 2 : bn)};
-    const cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = g_encode_tiled(&tmap_w, tmap_dtype(x.dtype), 2, const_cast<void*>(w_ptr), gdim, gstr,
-                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, tmap_swizzle(chunk_bytes),
-                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-      TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled failed with %d (Kgemm=%lld K=%lld bn=%d)", (int)r,
-              Kgemm, K, bn);
-  }
 
-  // ---- kernel arguments
+  // ---- kernel arguments common to every launch
   ConvKernelArgs a;
   memset(&a, 0, sizeof(a));
-  a.M = static_cast<int>(M);
   a.K_out = static_cast<int>(K);
   a.Ho = static_cast<int>(Ho);
   a.Wo = static_cast<int>(Wo);
@@ -720,12 +753,11 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   a.total_chunks = static_cast<int>(total_chunks_ll);
   a.C = static_cast<int>(Cg);
   a.a_tiled = a_tiled ? 1 : 0;
-  a.prefetch_dist = env_int("TRACEA_B200_PREFETCH", 0);
-  a.num_m_tiles = static_cast<int>(m_tiles);
+  a.prefetch_dist = knobs().prefetch;
   a.num_n_tiles = static_cast<int>(n_tiles);
-  a.num_stages = stages;
-  const uint32_t fmt = x.dtype == TRACEA_DTYPE_FLOAT16 ? 0u : (x.dtype == TRACEA_DTYPE_BFLOAT16 ? 1u : 2u);
-  a.idesc = tb200::ptx::make_idesc(fmt, pair ? 2 * tb200::kBlockM : tb200::kBlockM, bn);
+  a.b_k0 = static_cast<int>(b_k0);
+  a.b_jump_s = static_cast<int>(b_jump_s);
+  a.b_jump_r = static_cast<int>(b_jump_r);
   // K-major operand descriptors. Swizzled rows of chunk_bytes: 8-row groups are 8*chunk_bytes apart
   // (SBO) and one MMA (32 B of K) stays inside a row. Unswizzled 16-byte chunks: an 8-row x 16 B core
   // matrix is 128 contiguous bytes (SBO) and the MMA's second K half is the next chunk (LBO).
@@ -762,7 +794,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   // Output rows that are linear in m = (n*Ho + ho)*Wo + wo form a [M][pitch] matrix: the epilogue
   // stages 32-pixel x 128-byte boxes in shared memory and the TMA unit writes them out.
   const bool out_rows_linear = out.stride[2] == Wo * out.stride[3] && out.stride[0] == Ho * out.stride[2];
-  if (a.out_vec && out_rows_linear && env_int("TRACEA_B200_NO_TMA_STORE", 0) == 0) {
+  if (a.out_vec && out_rows_linear && knobs().no_tma_store == 0) {
     const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
     const cuuint64_t gstr[1] = {(cuuint64_t)(out.stride[3] * es)};
     const cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32u};
@@ -787,7 +819,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     // a residual with the same dense row-linear form is TMA-loaded into the epilogue's staging boxes
     const bool res_rows_linear = residual->stride[2] == Wo * residual->stride[3] &&
                                  residual->stride[0] == Ho * residual->stride[2];
-    if (a.out_tma && a.res_vec && res_rows_linear && env_int("TRACEA_B200_NO_TMA_RESIDUAL", 0) == 0) {
+    if (a.out_tma && a.res_vec && res_rows_linear && knobs().no_tma_residual == 0) {
       const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
       const cuuint64_t gstr[1] = {(cuuint64_t)(residual->stride[3] * es)};
       const cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32u};
@@ -809,21 +841,57 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     a.prof = pp != nullptr ? reinterpret_cast<long long*>(strtoull(pp, nullptr, 0)) : nullptr;
   }
 #endif
+  const uint32_t fmt = x.dtype == TRACEA_DTYPE_FLOAT16 ? 0u : (x.dtype == TRACEA_DTYPE_BFLOAT16 ? 1u : 2u);
 
-  const long long tiles = m_tiles * n_tiles;
-  const int grid = pair ? 2 * static_cast<int>(std::min<long long>(tiles, st.num_sms / 2))
-                        : static_cast<int>(std::min<long long>(tiles, st.num_sms));
-  switch (x.dtype) {
-    case TRACEA_DTYPE_BFLOAT16:
-      launch_bn<__nv_bfloat16>(st, 0, bn, pair, rows2, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
-      break;
-    case TRACEA_DTYPE_FLOAT16:
-      launch_bn<__half>(st, 1, bn, pair, rows2, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
-      break;
-    default:
-      launch_bn<float>(st, 2, bn, pair, rows2, tmap_x, tmap_w, tmap_out, tmap_res, a, grid, smem, stream);
-      break;
-  }
+  // ---- one launch over output pixels [row_begin, row_end) with the given tiling. (Splitting a partly filled last
+  // wave off into a second launch with 128-row tiles was measured and is slower: a CTA pair's 256-row tile costs
+  // each SM exactly what a 128-row tile costs it, so the tail does not get shorter, and the launch boundary adds
+  // ~10 us.)
+  auto launch_rows = [&](bool pair_v, bool rows2_v, long long row_begin, long long row_end) {
+    const long long rows = row_end - row_begin;
+    const long long tile_rows = (pair_v || rows2_v) ? 2 * tb200::kBlockM : tb200::kBlockM;
+    const long long m_tiles = (rows + tile_rows - 1) / tile_rows;
+    if (m_tiles * n_tiles > 0x7fffffffLL) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "too many tiles");
+    int stages = pick_stages(bn, pair_v, rows2_v);
+    const int forced_stages = knobs().force_stages;
+    if (forced_stages >= 2 && forced_stages <= stages) stages = forced_stages;
+    const int smem = tb200::conv_smem_bytes(bn, stages, pair_v, rows2_v);
+
+    CUtensorMap tmap_w;
+    // repacked or dense weights: one row is the whole Kgemm axis; in-place strided taps: one row spans the taps
+    const cuuint64_t gdim[2] = {(cuuint64_t)(w_remap ? w_row_elems : Kgemm), (cuuint64_t)K};
+    const cuuint64_t gstr[1] = {(cuuint64_t)((w_remap ? w_pitch : Kgemm) * es)};
+    const cuuint32_t box[2] = {(cuuint32_t)chunk_elems, (cuuint32_t)(pair_v ? bn / 2 : bn)};
+    const cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = g_encode_tiled(&tmap_w, tmap_dtype(x.dtype), 2, const_cast<void*>(w_ptr), gdim, gstr,
+                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, tmap_swizzle(chunk_bytes),
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled failed with %d (Kgemm=%lld K=%lld bn=%d)", (int)r,
+              Kgemm, K, bn);
+
+    ConvKernelArgs la = a;
+    la.m_begin = static_cast<int>(row_begin);
+    la.M = static_cast<int>(row_end);
+    la.num_m_tiles = static_cast<int>(m_tiles);
+    la.num_stages = stages;
+    la.idesc = tb200::ptx::make_idesc(fmt, pair_v ? 2 * tb200::kBlockM : tb200::kBlockM, bn);
+    const long long tiles = m_tiles * n_tiles;
+    const int grid = pair_v ? 2 * static_cast<int>(std::min<long long>(tiles, st.num_sms / 2))
+                            : static_cast<int>(std::min<long long>(tiles, st.num_sms));
+    switch (x.dtype) {
+      case TRACEA_DTYPE_BFLOAT16:
+        launch_bn<__nv_bfloat16>(st, 0, bn, pair_v, rows2_v, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
+        break;
+      case TRACEA_DTYPE_FLOAT16:
+        launch_bn<__half>(st, 1, bn, pair_v, rows2_v, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
+        break;
+      default:
+        launch_bn<float>(st, 2, bn, pair_v, rows2_v, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
+        break;
+    }
+  };
+  launch_rows(pair, rows2, 0, M);
 }
 
 // ------------------------------------------------------------------ host-memory staging
@@ -1365,6 +1433,7 @@ void launch_weight_pack(const void* src, void* dst, int es, long long K, long lo
         stride[0], stride[1], stride[2], stride[3]);
   }
   TB_CUDA(cudaGetLastError());
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
 void conv2d_prepack_checked(const TraceaTensorView& wv, void* dst, uint64_t dst_bytes, uint64_t* packed_shape,
@@ -1544,6 +1613,8 @@ void tracea_shutdown(void) {
     cudaSetDevice(prev);
   }
 }
+
+uint64_t tracea_b200_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 uint32_t tracea_b200_device_status(int32_t device_id) {
   if (device_id < 0 || device_id >= kMaxDevices) return 0;
