@@ -340,6 +340,15 @@ def run_ours(args):
         except Exception as e:  # the extra figure must never take the headline line down
             extra = {"error": "%s: %s" % (type(e).__name__, e)}
 
+    # ---- the operators either side of the conv path (GEMM, ConvTranspose2d), rank 0's GPU only, extra figures
+    next_ops = {}
+    if rank == 0 and not args.no_next_ops:
+        try:
+            next_ops = time_next_ops(dev, stream, lib, args.library_compare)
+        except Exception as e:
+            next_ops = {"error": "%s: %s" % (type(e).__name__, e)}
+    barrier()
+
     if rank == 0:
         peaks = load_peaks()
         total_s = elapsed_max * 1e-3
@@ -372,6 +381,7 @@ def run_ours(args):
             "gpu_launches_per_step": launches / steps,
             "clocks": clocks.summary(),
             "resnet50": extra,
+            "next_ops": next_ops,
         }
         if world == 1 and not args.no_cpu_baseline:
             tf, ms, threads, done = time_cpu_baseline(8, 1000, 1, budget_s=12.0)
@@ -385,6 +395,61 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def time_next_ops(dev, stream, lib, library_compare=False):
+    """GEMM and ConvTranspose2d through tracea_gemm / tracea_conv_transpose2d on device tensors: 5 warm-up calls,
+    then 20 timed calls between two CUDA events. Operand sets are larger than L2 (GEMM: 3 x 134 MB; the transposed
+    convolution: 67 MB in, 134 MB out). FLOPs: 2*M*N*K; for the transposed convolution 2 * input pixels * C * K * R * S
+    (every input pixel meets every tap once)."""
+    from tracea_b200 import ffi, ops
+
+    def timed(fn, iters=20, warm=5):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = lib.tracea_b200_launch_count()
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / iters, (lib.tracea_b200_launch_count() - before) // iters
+
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(5)
+    M = K = N = 8192
+    a = torch.randn((M, K), device=dev, dtype=torch.bfloat16, generator=g)
+    bt = torch.randn((N, K), device=dev, dtype=torch.bfloat16, generator=g)       # [N][K] memory = b (K, N), strides (1, K)
+    c = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+    va, vb, vc = ops._view(a), ops._view(bt.t()), ops._view(c)
+    ms, launches = timed(lambda: ffi.gemm_raw(va, vb, None, None, vc, ffi.EPILOGUE_IDENTITY, stream.cuda_stream))
+    peaks = load_peaks()
+    tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    out["gemm"] = {"workload": "bf16 8192 x 8192 x 8192, b read in place as [N][K]", "ms": ms, "tflops": tf,
+                   "launches_per_call": launches, "frac_of_measured_bf16_peak": tf / peaks["bf16_tflops"]}
+    if library_compare:
+        ms_lib, _ = timed(lambda: torch.matmul(a, bt.t(), out=c))
+        out["gemm"]["cublas_tflops"] = 2.0 * M * N * K / (ms_lib * 1e-3) / 1e12
+    del a, bt, c
+
+    n, h, w, cin, kout, r, st, pad = 128, 32, 32, 256, 128, 4, 2, 1
+    x = torch.randn((n, h, w, cin), device=dev, dtype=torch.bfloat16, generator=g)
+    wt = torch.randn((kout, r, r, cin), device=dev, dtype=torch.bfloat16, generator=g) * (cin * r * r) ** -0.5
+    ho = (h - 1) * st - 2 * pad + r
+    y = torch.empty((n, ho, ho, kout), device=dev, dtype=torch.bfloat16)
+    vx, vw, vy = ops._view(x), ops._view(wt), ops._view(y)
+    ms, launches = timed(lambda: ffi.conv_transpose2d_raw(vx, vw, None, None, vy, (st, st), (pad, pad), (0, 0), (1, 1), 1,
+                                                          ffi.EPILOGUE_IDENTITY, stream.cuda_stream))
+    flops = 2.0 * n * h * w * cin * kout * r * r
+    out["conv_transpose2d"] = {"workload": "bf16 x[128,32,32,256] * w[128,4,4,256], stride 2, pad 1 -> [128,64,64,128]",
+                               "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "launches_per_call": launches}
+    if library_compare:
+        xc, wc = x.permute(0, 3, 1, 2), wt.permute(3, 0, 1, 2).contiguous(memory_format=torch.channels_last)
+        ms_lib, _ = timed(lambda: torch.nn.functional.conv_transpose2d(xc, wc, None, st, pad))
+        out["conv_transpose2d"]["cudnn_tflops"] = flops / (ms_lib * 1e-3) / 1e12
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -394,6 +459,9 @@ def main():
     ap.add_argument("--no-resnet", action="store_true", help="skip the ResNet-50 conv-stack extra figure")
     ap.add_argument("--resnet-batch", type=int, default=512, help="global batch of the conv-stack figure")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-next-ops", action="store_true", help="skip the GEMM / ConvTranspose2d extra figures")
+    ap.add_argument("--library-compare", action="store_true",
+                    help="also time torch.matmul / torch conv_transpose2d (cuBLAS / cuDNN) on the same shapes, for context")
     ap.add_argument("--no-graph", action="store_true", help="launch the conv stack eagerly instead of from a CUDA graph")
     ap.add_argument("--only-layer", choices=["c1", "c2", "c3"], default=None,
                     help="profiling aid: only launch this layer of the block, print no JSON")

@@ -69,6 +69,8 @@ struct ConvKernelArgs {
   int prefetch_dist;      // > 0: the producer L2-prefetches A this many k-steps ahead of its loads
   // tiling / pipeline
   int num_m_tiles, num_n_tiles;
+  int panel_width;  // column tiles per panel of the tile order (>= 1; num_n_tiles = one panel = row-major order)
+  int panel_tiles;  // num_m_tiles * panel_width
   int num_stages;
   // tcgen05 descriptors (host-built constants)
   uint32_t idesc;
@@ -437,11 +439,17 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int chunks_per_stage = kStageKBytes / args.chunk_bytes;
   const int k_iters = (args.total_chunks + chunks_per_stage - 1) / chunks_per_stage;
 
-  // Tiles are walked as (m_tile, n_tile) pairs advanced without divisions: tile += num_workers.
-  const int tile_step_m = num_workers / args.num_n_tiles;
-  const int tile_step_n = num_workers % args.num_n_tiles;
-  const int first_m_tile = worker / args.num_n_tiles;
-  const int first_n_tile = worker % args.num_n_tiles;
+  // Tile order: the output is cut into panels of `panel_width` column tiles; inside a panel tiles run row by row.
+  // One wave of CTAs then works on a block of rows x panel_width columns whose A rows and B columns stay in L2
+  // (with a single panel -- panel_width = num_n_tiles -- this is plain row-major order). Two divisions per tile.
+  auto tile_coords = [&](int tile, int& mt, int& nt) {
+    const int panel = tile / args.panel_tiles;
+    const int rem = tile - panel * args.panel_tiles;
+    const int n0 = panel * args.panel_width;
+    const int width = min(args.panel_width, args.num_n_tiles - n0);
+    mt = rem / width;
+    nt = n0 + rem - mt * width;
+  };
   const uint32_t full_bar0 = bar_base, empty_bar0 = bar_base + 8u * kMaxStages;
   const uint32_t full_leader0 = kPair ? mapa_cluster(full_bar0, 0u) : full_bar0;   // leader's full barriers
   const uint32_t ring_end = smem_base + ring_bytes;
@@ -459,7 +467,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const bool one_chunk = (chunks_per_stage == 1) && !args.a_tiled;
       bool ok = true;
       int issued = 0;
-      int m_tile = first_m_tile, n_tile = first_n_tile;
+      int m_tile = 0, n_tile = 0;
       long long prof_wait = 0;
       (void)prof_wait;
       TB200_PROF_T(prof_t0);
@@ -470,6 +478,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         uint32_t off_w, off_h;
       } pf = {};
       auto pf_begin_tile = [&]() {
+        tile_coords(pf.tile, pf.m_tile, pf.n_tile);
         const int pm0 = args.m_begin + pf.m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
         const int pt = pm0 / args.Wo;
         pf.w_start = (pm0 % args.Wo) * args.stride_w - args.pad_w;
@@ -489,18 +498,17 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         if (++pf.it == k_iters) {
           pf.tile += num_workers;
-          pf.n_tile += tile_step_n; pf.m_tile += tile_step_m;
-          if (pf.n_tile >= args.num_n_tiles) { pf.n_tile -= args.num_n_tiles; ++pf.m_tile; }
           if (pf.tile < num_tiles) pf_begin_tile();
         }
       };
       const bool do_prefetch = one_chunk && args.prefetch_dist > 0;
       if (do_prefetch) {
-        pf.tile = worker; pf.m_tile = first_m_tile; pf.n_tile = first_n_tile;
+        pf.tile = worker;
         if (pf.tile < num_tiles) pf_begin_tile();
         for (int i = 0; i < args.prefetch_dist; ++i) pf_step();
       }
       for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
+        tile_coords(tile, m_tile, n_tile);
         const int m0 = args.m_begin + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;   // this CTA's 128 pixels
         const int q0 = m0 % args.Wo;
         const int t = m0 / args.Wo;
@@ -600,8 +608,6 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
           slot_free = false;   // this path waits in full every time
         }
-        n_tile += tile_step_n; m_tile += tile_step_m;
-        if (n_tile >= args.num_n_tiles) { n_tile -= args.num_n_tiles; ++m_tile; }
       }
       TB200_PROF_STORE(0, prof_wait);
       TB200_PROF_STORE(1, clock64() - prof_t0);
@@ -761,14 +767,16 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // the worker, of which the group takes the 128-row block `egroup`
     const int etile0 = kRows2 ? worker : worker + egroup * num_workers;
     const int estride = kRows2 ? num_workers : 2 * num_workers;
-    const int estep_m = estride / args.num_n_tiles, estep_n = estride % args.num_n_tiles;
-    if (etile0 < num_tiles) fetch_bias(etile0 % args.num_n_tiles);
+    int m_tile = 0, n_tile = 0;
+    if (etile0 < num_tiles) {
+      tile_coords(etile0, m_tile, n_tile);
+      fetch_bias(n_tile);
+    }
     int local_tile = kRows2 ? 0 : egroup;
     bool ok = true;
     long long prof_wacc = 0, prof_wres = 0, prof_ld = 0, prof_math = 0, prof_stage = 0, prof_wstore = 0;
     (void)prof_wacc; (void)prof_wres; (void)prof_ld; (void)prof_math; (void)prof_stage; (void)prof_wstore;
     TB200_PROF_T(prof_t0);
-    int m_tile = etile0 / args.num_n_tiles - estep_m, n_tile = etile0 % args.num_n_tiles - estep_n;
     const bool need_coords = !args.out_tma || (res != nullptr && !res_tma);
     // Channel-contiguous outputs whose pixels are not one dense [M][pitch] matrix (a strided view, one phase of a
     // transposed convolution) take the same staging boxes as the TMA path, but the warp moves them itself:
@@ -776,9 +784,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const bool coop = !args.out_tma && args.out_vec != 0 && (res == nullptr || args.res_vec != 0);
     const bool res_staged = res_tma || (coop && res != nullptr);
     for (int tile = etile0; tile < num_tiles && ok; tile += estride, local_tile += (kRows2 ? 1 : 2)) {
-      n_tile += estep_n; m_tile += estep_m;
-      if (n_tile >= args.num_n_tiles) { n_tile -= args.num_n_tiles; ++m_tile; }
-      else if (n_tile < 0) { n_tile += args.num_n_tiles; --m_tile; }
+      tile_coords(tile, m_tile, n_tile);
       const int buf = kRows2 ? (local_tile & 1) : egroup;
       const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
       const int n_base = n_tile * BN;
@@ -794,10 +800,10 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         __syncwarp();
         bias_tile = n_tile;
       }
-      if (tile + estride < num_tiles && estep_n != 0) {
-        int nn = n_tile + estep_n;
-        if (nn >= args.num_n_tiles) nn -= args.num_n_tiles;
-        fetch_bias(nn);
+      if (tile + estride < num_tiles) {
+        int mm, nn;
+        tile_coords(tile + estride, mm, nn);
+        if (nn != n_tile) fetch_bias(nn);
       }
 
       const int m = args.m_begin + m_tile * kTileM + row_block * kBlockM + row;

@@ -382,7 +382,7 @@ int env_int(const char* name, int dflt) {
 // part of the ~6 us a call costs on the host). TRACEA_B200_HOST_CHUNKS is read per call and is not in here.
 struct Knobs {
   int force_bn, force_stages, force_chunk, no_tma_store, no_tma_residual, tiled_a, force_staging, no_window, prefetch,
-      pair, rows2;
+      pair, rows2, panel;
 };
 const Knobs& knobs() {
   static const Knobs k = {
@@ -391,7 +391,7 @@ const Knobs& knobs() {
       env_int("TRACEA_B200_NO_TMA_RESIDUAL", 0), env_int("TRACEA_B200_TILED_A", 0),
       env_int("TRACEA_B200_FORCE_STAGING", 0), env_int("TRACEA_B200_NO_WINDOW", 0),
       env_int("TRACEA_B200_PREFETCH", 0),      env_int("TRACEA_B200_PAIR", -1),
-      env_int("TRACEA_B200_ROWS2", -1)};
+      env_int("TRACEA_B200_ROWS2", -1),        env_int("TRACEA_B200_PANEL", 0)};
   return k;
 }
 
@@ -874,6 +874,13 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     la.m_begin = static_cast<int>(row_begin);
     la.M = static_cast<int>(row_end);
     la.num_m_tiles = static_cast<int>(m_tiles);
+    // Tile order: wide outputs are walked in panels of 8 column tiles so that a wave of CTAs shares its B columns
+    // and A rows through L2 instead of streaming all of B once per wave (TRACEA_B200_PANEL overrides the width).
+    long long panel = n_tiles > 8 ? 8 : n_tiles;
+    if (knobs().panel > 0) panel = std::min<long long>(knobs().panel, n_tiles);
+    if (m_tiles * panel > 0x7fffffffLL) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "too many tiles");
+    la.panel_width = static_cast<int>(panel);
+    la.panel_tiles = static_cast<int>(m_tiles * panel);
     la.num_stages = stages;
     la.idesc = tb200::ptx::make_idesc(fmt, pair_v ? 2 * tb200::kBlockM : tb200::kBlockM, bn);
     const long long tiles = m_tiles * n_tiles;
