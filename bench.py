@@ -400,6 +400,7 @@ def time_next_ops(dev, stream, lib, library_compare=False):
     then 20 timed calls between two CUDA events. Operand sets are larger than L2 (GEMM: 3 x 134 MB; the transposed
     convolution: 67 MB in, 134 MB out). FLOPs: 2*M*N*K; for the transposed convolution 2 * input pixels * C * K * R * S
     (every input pixel meets every tap once)."""
+    import torch
     from tracea_b200 import ffi, ops
 
     def timed(fn, iters=20, warm=5):
