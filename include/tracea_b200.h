@@ -192,6 +192,16 @@ TraceaStatus tracea_conv_transpose2d(TraceaTensorView x, TraceaTensorView w, con
                                      const TraceaTensorView *residual, TraceaTensorView *out,
                                      TraceaConvTranspose2dParams params);
 
+/* The plan tracea_conv_transpose2d follows along one axis, for inspection and tests (pure arithmetic, no device).
+ * For each output phase a0 in [0, stride) it writes 8 values to phases[8*a0 ..]:
+ *   {a0, T, a, taps, x_off, in, pad_lo, pad_hi}
+ * outputs a0 + stride*t, t < T, are a stride-1 correlation of input rows [x_off, x_off + in), zero-padded by pad_lo
+ * in front and pad_hi behind, with the `taps` filter taps a + stride*(taps-1-j), j = 0..taps-1 (reversed order);
+ * a = -1 marks a phase no tap reaches (one zero tap). T = 0: the phase has no outputs. Returns stride, or -1 on
+ * bad arguments. No counterpart in the reference. */
+int32_t tracea_b200_conv_transpose_plan(uint32_t in_extent, uint32_t out_extent, uint32_t filter, uint32_t stride,
+                                        uint32_t padding, int64_t *phases);
+
 /* Weight prepacking, so that the documented OIHW / row-major surface costs nothing in steady state. No
  * counterpart in the reference, whose kernels fix one weight layout per back end (src/emitter/cuda/conv.rs:248-266).
  *

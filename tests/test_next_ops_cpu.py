@@ -131,3 +131,48 @@ def test_prepack_validation(lib):
     st2 = (ctypes.c_int64 * 2)()
     assert lib.tracea_gemm_prepack_b(_view(b, device=0).c, 16, 10, st2, None) == ffi.INVALID_PARAMS
     assert "needs" in ffi.last_error()
+
+
+# --------------------------------------------------------------------------- the phase plan (host arithmetic)
+def _replay_plan_1d(x, w, stride, pad, opad):
+    """x: (H,), w: (R,). Runs the library's per-phase plan as plain stride-1 correlations and scatters the phases."""
+    H, R = len(x), len(w)
+    Ho = (H - 1) * stride - 2 * pad + R + opad
+    out = np.full(Ho, np.nan)
+    for ph in ffi.conv_transpose_plan(H, Ho, R, stride, pad):
+        if ph["T"] == 0:
+            continue
+        if ph["a"] < 0:
+            taps = np.zeros(1)
+        else:
+            taps = np.array([w[ph["a"] + stride * (ph["taps"] - 1 - j)] for j in range(ph["taps"])])
+        assert ph["in"] >= 1 and ph["pad_lo"] >= 0 and ph["pad_hi"] >= 0 and ph["x_off"] + ph["in"] <= H
+        assert ph["T"] == ph["in"] + ph["pad_lo"] + ph["pad_hi"] - (ph["taps"] - 1)
+        xp = np.concatenate([np.zeros(ph["pad_lo"]), x[ph["x_off"]:ph["x_off"] + ph["in"]], np.zeros(ph["pad_hi"])])
+        vals = np.array([np.dot(xp[t:t + ph["taps"]], taps) for t in range(ph["T"])])
+        out[ph["a0"]::stride] = vals
+    assert not np.isnan(out).any()          # the phases cover every output exactly
+    return out
+
+
+@pytest.mark.parametrize("H,R,stride,pad,opad", [
+    (5, 3, 1, 0, 0), (5, 3, 1, 1, 0), (6, 5, 1, 3, 0), (4, 2, 2, 0, 0), (5, 3, 2, 1, 1), (8, 4, 2, 1, 0),
+    (5, 2, 3, 0, 1), (5, 2, 3, 0, 2), (7, 5, 3, 2, 1), (3, 7, 2, 3, 1), (9, 1, 2, 0, 1), (6, 3, 4, 1, 3),
+    (2, 6, 5, 2, 4), (10, 4, 2, 3, 0), (1, 3, 2, 1, 1),
+])
+def test_phase_plan_reproduces_the_transposed_convolution(H, R, stride, pad, opad):
+    if (H - 1) * stride - 2 * pad + R + opad <= 0:
+        pytest.skip("empty output")
+    rng = cc.rng_for(1, "plan/%d/%d/%d/%d/%d" % (H, R, stride, pad, opad))
+    x, w = rng.standard_normal(H), rng.standard_normal(R)
+    got = _replay_plan_1d(x, w, stride, pad, opad)
+    want = oracle.conv_transpose2d(x.astype(np.float32).reshape(1, H, 1, 1), w.astype(np.float32).reshape(1, R, 1, 1),
+                                   None, None, (stride, 1), (pad, 0), (opad, 0)).reshape(-1)
+    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+
+
+def test_phase_plan_rejects_bad_arguments(lib):
+    import ctypes
+    buf = (ctypes.c_int64 * 16)()
+    assert lib.tracea_b200_conv_transpose_plan(4, 8, 3, 0, 0, buf) == -1
+    assert lib.tracea_b200_conv_transpose_plan(4, 8, 3, 2, 0, None) == -1

@@ -168,6 +168,17 @@ def test_gemm_operand_layouts_give_identical_results(layout):
     assert torch.equal(other, base)
 
 
+@pytest.mark.parametrize("shape", [(700, 256, 4096), (300, 128, 2560 + 64), (129, 64, 9 * 256 + 8)])
+def test_gemm_wide_outputs_walk_the_tiles_in_panels(shape):
+    """More than 8 column tiles: the kernel walks panels of 8 (the last one narrower); every tile is still visited once."""
+    M, K, N = shape
+    a = cc.normal((M, K), 12, "gw/a")
+    bm = cc.normal((K, N), 12, "gw/b", K ** -0.5)
+    bias = cc.normal((N,), 12, "gw/bias", 0.1)
+    got = host(ops.gemm(dev(a, "bf16"), dev(bm, "bf16"), torch.from_numpy(bias).cuda(), "bias"))
+    assert cc.rel_err(got, gemm_want(a, bm, bias, None, "bias", "bf16")) <= cc.TOL_16BIT
+
+
 def test_gemm_reads_a_padded_pitch_b_in_place():
     M, K, N = 300, 128, 72
     a = dev(cc.normal((M, K), 8, "gp/a"), "bf16")

@@ -1621,6 +1621,19 @@ void tracea_shutdown(void) {
   }
 }
 
+int32_t tracea_b200_conv_transpose_plan(uint32_t in_extent, uint32_t out_extent, uint32_t filter, uint32_t stride,
+                                        uint32_t padding, int64_t* phases) {
+  if (phases == nullptr || stride == 0 || stride > 16 || in_extent == 0 || filter == 0) return -1;
+  for (uint32_t a0 = 0; a0 < stride; ++a0) {
+    PhaseAxis ax = phase_axis(in_extent, out_extent, filter, stride, padding, a0);
+    if (ax.T > 0 && ax.empty) make_empty_axis(ax, in_extent);
+    int64_t* o = phases + 8 * a0;
+    o[0] = ax.a0; o[1] = ax.T; o[2] = ax.a; o[3] = ax.taps; o[4] = ax.x_off; o[5] = ax.in; o[6] = ax.pad_lo; o[7] = ax.pad_hi;
+    if (ax.T > 0 && ax.empty) o[2] = -1;   // no tap reaches this phase: its single tap is a zero
+  }
+  return static_cast<int32_t>(stride);
+}
+
 uint64_t tracea_b200_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 uint32_t tracea_b200_device_status(int32_t device_id) {

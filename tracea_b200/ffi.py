@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "tracea_conv2d", "tracea_conv2d_v0", "tracea_conv2d_noalloc", "tracea_get_last_error", "tracea_clear_error",
     "tracea_version_major", "tracea_version_minor", "tracea_version_patch", "tracea_init",
     "tracea_shutdown", "tracea_b200_device_status", "tracea_b200_launch_count",
+    "tracea_b200_conv_transpose_plan",
     "tracea_gemm", "tracea_conv_transpose2d", "tracea_conv2d_prepack_bytes", "tracea_conv2d_prepack",
     "tracea_gemm_prepack_b_bytes", "tracea_gemm_prepack_b",
 )
@@ -123,6 +124,8 @@ def load():
     lib.tracea_b200_device_status.restype = ctypes.c_uint32
     lib.tracea_b200_launch_count.argtypes = []
     lib.tracea_b200_launch_count.restype = ctypes.c_uint64
+    lib.tracea_b200_conv_transpose_plan.argtypes = [ctypes.c_uint32] * 5 + [ctypes.POINTER(ctypes.c_int64)]
+    lib.tracea_b200_conv_transpose_plan.restype = ctypes.c_int32
     pv = ctypes.POINTER(TensorView)
     lib.tracea_gemm.argtypes = [TensorView, TensorView, pv, pv, pv, GemmParams]
     lib.tracea_gemm.restype = ctypes.c_int
@@ -197,3 +200,12 @@ def conv_transpose2d_raw(x, w, bias, residual, out, stride=(1, 1), padding=(0, 0
     if check and st != SUCCESS:
         raise TraceaError(st, last_error(), "tracea_conv_transpose2d")
     return st
+
+
+def conv_transpose_plan(in_extent, out_extent, filt, stride, padding):
+    """Per-phase geometry tracea_conv_transpose2d uses along one axis: a list of dicts, one per phase."""
+    buf = (ctypes.c_int64 * (8 * stride))()
+    if load().tracea_b200_conv_transpose_plan(in_extent, out_extent, filt, stride, padding, buf) != stride:
+        raise ValueError("bad arguments")
+    keys = ("a0", "T", "a", "taps", "x_off", "in", "pad_lo", "pad_hi")
+    return [dict(zip(keys, buf[8 * i:8 * i + 8])) for i in range(stride)]
