@@ -221,3 +221,29 @@ def test_prepacked_conv_weights_are_read_in_place_with_identical_results(shape):
     a = ops.conv2d_nchw(x, w, None, None, 1, R // 2)
     b = ops.conv2d_nchw(xp, packed, None, None, 1, R // 2)
     assert torch.equal(a, b)
+
+
+# --------------------------------------------------------------------------- torch.nn front end
+@pytest.mark.parametrize("cfg", [dict(cin=64, cout=96, k=3, stride=1, padding=1, bias=True),
+                                 dict(cin=3, cout=32, k=7, stride=2, padding=3, bias=False),
+                                 dict(cin=32, cout=64, k=3, stride=1, padding=2, dilation=2, bias=True)])
+def test_nn_module_is_a_drop_in_for_conv2d(cfg):
+    from tracea_b200 import nn as tnn
+    torch.manual_seed(3)
+    m = tnn.TraceaConv2d(cfg["cin"], cfg["cout"], cfg["k"], stride=cfg["stride"], padding=cfg["padding"],
+                         dilation=cfg.get("dilation", 1), bias=cfg["bias"]).cuda().to(torch.bfloat16)
+    x = torch.randn(2, cfg["cin"], 20, 20, device="cuda", dtype=torch.bfloat16)
+    before = ffi.load().tracea_b200_launch_count()
+    y1 = m(x)
+    first = ffi.load().tracea_b200_launch_count() - before
+    y2 = m(x.contiguous(memory_format=torch.channels_last))
+    second = ffi.load().tracea_b200_launch_count() - before - first
+    assert torch.equal(y1, y2.contiguous())
+    if cfg["cin"] % 8 == 0:
+        assert second == 1                       # packed weights cached, channels-last input: the conv kernel only
+    want = oracle.conv2d(x.float().cpu().numpy(), m.weight.detach().float().cpu().numpy(),
+                         m.bias.detach().float().cpu().numpy() if cfg["bias"] else None, None, cfg["stride"],
+                         cfg["padding"], cfg.get("dilation", 1), "none")
+    assert cc.rel_err(host(y1), cc.round_to(want, "bf16")) <= cc.TOL_16BIT
+    with pytest.raises(NotImplementedError):
+        tnn.TraceaConv2d(8, 8, 3, groups=2).cuda()(torch.randn(1, 8, 5, 5, device="cuda"))

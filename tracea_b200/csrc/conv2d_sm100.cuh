@@ -72,6 +72,7 @@ struct ConvKernelArgs {
   int panel_width;  // column tiles per panel of the tile order (>= 1; num_n_tiles = one panel = row-major order)
   int panel_tiles;  // num_m_tiles * panel_width
   int num_stages;
+  int shared_bias;  // 1: one bias copy per CTA (num_n_tiles == 1) instead of one per epilogue warp
   // tcgen05 descriptors (host-built constants)
   uint32_t idesc;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo, swizzle_mode;
@@ -158,7 +159,8 @@ __device__ __forceinline__ void report_error(const ConvKernelArgs& a, volatile u
 //   [0, stages * stage_bytes)        operand ring: per stage A (128 rows x 128 B) then B (BN rows x 128 B)
 //   + kStagingBytes                  per epilogue warp 2 alternating 4 KB boxes (32 pixels x 128 B): the residual
 //                                    is TMA-loaded into a box, combined in place, and the box is TMA-stored
-//   + 8 * BN * 4                     per-epilogue-warp copy of the tile's bias, as fp32
+//   + 8 * BN * 4                     per-epilogue-warp copy of the tile's bias, as fp32 (one BN * 4 copy for the
+//                                    whole CTA when the output is a single tile wide: the bias never changes)
 //   + 256                            mbarriers, TMEM base slot, abort flag
 constexpr int kStagingBoxBytes = 32 * 128;
 constexpr int kStagingDepth = 2;
@@ -166,9 +168,10 @@ constexpr int kNumEpilogueWarps = 8;
 constexpr int kStagingBytes = kNumEpilogueWarps * kStagingDepth * kStagingBoxBytes;
 // `pair`: two CTAs on neighbouring SMs work on one 256-row tile and each holds only half of B's rows.
 // `rows2`: one CTA owns a 256-row tile (two 128-row blocks of A per stage against one B).
-__host__ __device__ constexpr int conv_smem_bytes(int bn, int stages, bool pair = false, bool rows2 = false) {
+__host__ __device__ constexpr int conv_smem_bytes(int bn, int stages, bool pair = false, bool rows2 = false,
+                                                  bool shared_bias = false) {
   return stages * ((rows2 ? 2 : 1) * kBlockM * kStageKBytes + (pair ? bn / 2 : bn) * kStageKBytes) + kStagingBytes +
-         kNumEpilogueWarps * bn * 4 + 512 + 1024;
+         (shared_bias ? 1 : kNumEpilogueWarps) * bn * 4 + 512 + 1024;
 }
 
 // 8 consecutive fp32 values -> one 16-byte vector of OutT (16-bit types) / 4 values (fp32).
@@ -367,7 +370,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t ring_bytes = static_cast<uint32_t>(num_stages) * kStageBytes;
   const uint32_t staging_base = smem_base + ring_bytes;
   const uint32_t bias_off = ring_bytes + kStagingBytes;
-  const uint32_t bar_off = bias_off + kNumEpilogueWarps * BN * 4u;
+  const uint32_t bar_off = bias_off + (args.shared_bias ? 1u : static_cast<uint32_t>(kNumEpilogueWarps)) * BN * 4u;
   const uint32_t bar_base = smem_base + bar_off;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
@@ -719,8 +722,10 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     constexpr int kGroups = BN / kGroupCols;
     constexpr int kLdPerGroup = kGroupCols / 32;
     constexpr int kChunksPerLd = 32 / kVec;        // 16-byte chunks produced per 32-column TMEM load
-    float* bias_w = reinterpret_cast<float*>(smem_gen + bias_off) + ew * BN;
-    const uint32_t bias_w_s = smem_base + bias_off + static_cast<uint32_t>(ew * BN) * 4u;
+    // with a shared copy every warp writes the same values to the same words before it reads them
+    const int bias_slot = args.shared_bias ? 0 : ew * BN;
+    float* bias_w = reinterpret_cast<float*>(smem_gen + bias_off) + bias_slot;
+    const uint32_t bias_w_s = smem_base + bias_off + static_cast<uint32_t>(bias_slot) * 4u;
     const uint32_t stg0 = staging_base + static_cast<uint32_t>(ew) * (kStagingDepth * kStagingBoxBytes);
     const bool res_tma = args.res_tma != 0;
     // this lane's 16-byte chunk c of its staging row lives at row*128 + ((c ^ (row & 7)) << 4): the

@@ -296,9 +296,9 @@ int pick_bn(long long m_tiles, int k_out, int num_sms) {
   return best;
 }
 
-int pick_stages(int bn, bool pair, bool rows2) {
+int pick_stages(int bn, bool pair, bool rows2, bool shared_bias) {
   const int stage_bytes = tb200::conv_smem_bytes(bn, 1, pair, rows2) - tb200::conv_smem_bytes(bn, 0, pair, rows2);
-  const int fixed = tb200::conv_smem_bytes(bn, 0, pair, rows2);
+  const int fixed = tb200::conv_smem_bytes(bn, 0, pair, rows2, shared_bias);
   int s = (232448 - fixed) / stage_bytes;  // 227 KB opt-in limit per CTA
   return std::min(s, tb200::kMaxStages);
 }
@@ -753,7 +753,11 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   a.total_chunks = static_cast<int>(total_chunks_ll);
   a.C = static_cast<int>(Cg);
   a.a_tiled = a_tiled ? 1 : 0;
-  a.prefetch_dist = knobs().prefetch;
+  // L2 prefetch of the activations a few k-steps ahead of the loads: pays only where A streams from HBM with
+  // no reuse and the k-loop is long (1x1 layers with >= 8 k-steps: -3 %); it slows 3x3 layers down (their A
+  // mostly hits L2 already). TRACEA_B200_PREFETCH=n forces a distance, -1 switches it off.
+  a.prefetch_dist = knobs().prefetch > 0 ? knobs().prefetch
+                    : (knobs().prefetch == 0 && R == 1 && S == 1 && total_chunks_ll >= 8 ? 4 : 0);
   a.num_n_tiles = static_cast<int>(n_tiles);
   a.b_k0 = static_cast<int>(b_k0);
   a.b_jump_s = static_cast<int>(b_jump_s);
@@ -852,10 +856,13 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     const long long tile_rows = (pair_v || rows2_v) ? 2 * tb200::kBlockM : tb200::kBlockM;
     const long long m_tiles = (rows + tile_rows - 1) / tile_rows;
     if (m_tiles * n_tiles > 0x7fffffffLL) TB_FAIL(TRACEA_UNSUPPORTED_CONFIG, "too many tiles");
-    int stages = pick_stages(bn, pair_v, rows2_v);
+    // an output one tile wide never changes its bias: one copy per CTA instead of one per epilogue warp leaves
+    // room for a fifth stage of the CTA-pair tiling
+    const bool shared_bias = n_tiles == 1;
+    int stages = pick_stages(bn, pair_v, rows2_v, shared_bias);
     const int forced_stages = knobs().force_stages;
     if (forced_stages >= 2 && forced_stages <= stages) stages = forced_stages;
-    const int smem = tb200::conv_smem_bytes(bn, stages, pair_v, rows2_v);
+    const int smem = tb200::conv_smem_bytes(bn, stages, pair_v, rows2_v, shared_bias);
 
     CUtensorMap tmap_w;
     // repacked or dense weights: one row is the whole Kgemm axis; in-place strided taps: one row spans the taps
@@ -882,6 +889,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     la.panel_width = static_cast<int>(panel);
     la.panel_tiles = static_cast<int>(m_tiles * panel);
     la.num_stages = stages;
+    la.shared_bias = shared_bias ? 1 : 0;
     la.idesc = tb200::ptx::make_idesc(fmt, pair_v ? 2 * tb200::kBlockM : tb200::kBlockM, bn);
     const long long tiles = m_tiles * n_tiles;
     const int grid = pair_v ? 2 * static_cast<int>(std::min<long long>(tiles, st.num_sms / 2))

@@ -151,16 +151,25 @@ def last_error():
     return buf.raw[:n].decode("utf-8", "replace") if n > 0 else ""
 
 
+_U64_ARRAYS = {n: ctypes.c_uint64 * n for n in range(0, 9)}
+_I64_ARRAYS = {n: ctypes.c_int64 * n for n in range(0, 9)}
+_NULL_STRIDE = ctypes.POINTER(ctypes.c_int64)()
+
+
 class View:
     """Owns the shape/stride arrays a TensorView borrows (the caller-owned arrays of
-    include/tracea.hpp:56-66)."""
+    include/tracea.hpp:56-66). Construction is on the per-call path of the Python surface, hence the
+    pre-built array types."""
 
     def __init__(self, ptr, shape, stride, dtype, device_id):
-        self._shape = (ctypes.c_uint64 * len(shape))(*[int(s) for s in shape])
-        self._stride = (ctypes.c_int64 * len(shape))(*[int(s) for s in stride]) if stride is not None else None
-        self.c = TensorView(ctypes.c_void_p(ptr), len(shape), self._shape,
-                            self._stride if self._stride is not None else ctypes.POINTER(ctypes.c_int64)(),
-                            int(dtype), int(device_id))
+        n = len(shape)
+        self._shape = _U64_ARRAYS[n](*shape)
+        if stride is not None:
+            self._stride = _I64_ARRAYS[n](*stride)
+            self.c = TensorView(ptr, n, self._shape, self._stride, dtype, device_id)
+        else:
+            self._stride = None
+            self.c = TensorView(ptr, n, self._shape, _NULL_STRIDE, dtype, device_id)
 
 
 def conv2d_raw(x, w, bias, residual, out, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1,

@@ -75,10 +75,11 @@ def _device_id(t):
 
 
 def _view(t, shape=None, stride=None):
-    if t.dtype not in _DTYPES:
+    dt = _DTYPES.get(t.dtype)
+    if dt is None:
         raise TypeError("unsupported dtype %s" % t.dtype)
-    return ffi.View(t.data_ptr(), tuple(t.shape) if shape is None else shape,
-                    tuple(t.stride()) if stride is None else stride, _DTYPES[t.dtype], _device_id(t))
+    return ffi.View(t.data_ptr(), t.shape if shape is None else shape, t.stride() if stride is None else stride, dt,
+                    t.device.index if t.is_cuda else -1)
 
 
 def _nchw_view_of_nhwc(t):
