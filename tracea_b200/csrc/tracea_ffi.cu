@@ -451,6 +451,40 @@ NoAllocState& noalloc_state(int dev) {
   return na;
 }
 
+// ------------------------------------------------------------------ weight packing
+// w[k, c, r, s] through element strides -> dst[k][r][Sd][Cp] (channels >= C and tap slots >= S zero-filled).
+void launch_weight_pack(const void* src, void* dst, int es, long long K, long long C, long long R, long long S,
+                        long long Sd, long long Cp, const long long stride[4], cudaStream_t stream) {
+  const long long total = K * R * Sd * Cp;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+  if (R == 1 && Sd == 1 && (Cp + 31) / 32 <= 65535) {
+    // a 1x1 filter is a [K][C] matrix: the tiled transpose keeps both sides coalesced when w arrives C-major
+    // (a row-major GEMM B operand)
+    dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>((Cp + 31) / 32), 1u);
+    dim3 block(32, 8);
+    if (es == 2)
+      tb200::to_channels_last_kernel<uint16_t><<<grid, block, 0, stream>>>(
+          static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), (int)C, 1, (int)K, (int)Cp, 0LL, stride[1], 0LL,
+          stride[0]);
+    else
+      tb200::to_channels_last_kernel<uint32_t><<<grid, block, 0, stream>>>(
+          static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), (int)C, 1, (int)K, (int)Cp, 0LL, stride[1], 0LL,
+          stride[0]);
+  } else if (es == 2) {
+    tb200::pack_weights_krsc_kernel<uint16_t><<<blocks, threads, 0, stream>>>(
+        static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), total, (int)C, (int)R, (int)S, (int)Sd, (int)Cp,
+        stride[0], stride[1], stride[2], stride[3]);
+  } else {
+    tb200::pack_weights_krsc_kernel<uint32_t><<<blocks, threads, 0, stream>>>(
+        static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), total, (int)C, (int)R, (int)S, (int)Sd, (int)Cp,
+        stride[0], stride[1], stride[2], stride[3]);
+  }
+  TB_CUDA(cudaGetLastError());
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+
 // ------------------------------------------------------------------ the device path
 // The conv geometry the kernel runs: the public parameters plus a separate padding behind the last row /
 // column. padding_h / padding_w pad in front; the output extents are out.shape[2], out.shape[3] and must equal
@@ -637,33 +671,8 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   }
   const long long Sd = window ? 8 : S;   // tap slots per filter row in the packed weights
   if (!w_direct || window) {
-    const long long total = K * R * Sd * Cp;
-    void* w_stage = staging(w_scratch, static_cast<size_t>(total) * es, "the repacked weights");
-    const int threads = 256;
-    const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
-    if (R == 1 && Sd == 1 && (Cp + 31) / 32 <= 65535) {
-      // a 1x1 filter is a [K][C] matrix: the tiled transpose keeps both sides coalesced when w arrives
-      // C-major (a row-major GEMM B operand)
-      dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>((Cp + 31) / 32), 1u);
-      dim3 block(32, 8);
-      if (es == 2)
-        tb200::to_channels_last_kernel<uint16_t><<<grid, block, 0, stream>>>(
-            static_cast<const uint16_t*>(w_in.ptr), static_cast<uint16_t*>(w_stage), (int)C, 1, (int)K, (int)Cp, 0LL,
-            w_in.stride[1], 0LL, w_in.stride[0]);
-      else
-        tb200::to_channels_last_kernel<uint32_t><<<grid, block, 0, stream>>>(
-            static_cast<const uint32_t*>(w_in.ptr), static_cast<uint32_t*>(w_stage), (int)C, 1, (int)K, (int)Cp, 0LL,
-            w_in.stride[1], 0LL, w_in.stride[0]);
-    } else if (es == 2)
-      tb200::pack_weights_krsc_kernel<uint16_t><<<blocks, threads, 0, stream>>>(
-          static_cast<const uint16_t*>(w_in.ptr), static_cast<uint16_t*>(w_stage), total, (int)C,
-          (int)R, (int)S, (int)Sd, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
-    else
-      tb200::pack_weights_krsc_kernel<uint32_t><<<blocks, threads, 0, stream>>>(
-          static_cast<const uint32_t*>(w_in.ptr), static_cast<uint32_t*>(w_stage), total, (int)C,
-          (int)R, (int)S, (int)Sd, (int)Cp, w_in.stride[0], w_in.stride[1], w_in.stride[2], w_in.stride[3]);
-    TB_CUDA(cudaGetLastError());
-    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    void* w_stage = staging(w_scratch, static_cast<size_t>(K * R * Sd * Cp) * es, "the repacked weights");
+    launch_weight_pack(w_in.ptr, w_stage, es, K, C, R, S, Sd, Cp, w_in.stride, stream);
     w_ptr = w_stage;
   }
 
@@ -1422,35 +1431,6 @@ long long padded_channels(long long c, int es) {
   return (c + v - 1) / v * v;
 }
 
-void launch_weight_pack(const void* src, void* dst, int es, long long K, long long C, long long R, long long S,
-                        long long Cp, const long long stride[4], cudaStream_t stream) {
-  const long long total = K * R * S * Cp;
-  const int threads = 256;
-  const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
-  if (R == 1 && S == 1 && (Cp + 31) / 32 <= 65535) {
-    dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>((Cp + 31) / 32), 1u);
-    dim3 block(32, 8);
-    if (es == 2)
-      tb200::to_channels_last_kernel<uint16_t><<<grid, block, 0, stream>>>(
-          static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), (int)C, 1, (int)K, (int)Cp, 0LL, stride[1], 0LL,
-          stride[0]);
-    else
-      tb200::to_channels_last_kernel<uint32_t><<<grid, block, 0, stream>>>(
-          static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), (int)C, 1, (int)K, (int)Cp, 0LL, stride[1], 0LL,
-          stride[0]);
-  } else if (es == 2) {
-    tb200::pack_weights_krsc_kernel<uint16_t><<<blocks, threads, 0, stream>>>(
-        static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), total, (int)C, (int)R, (int)S, (int)S, (int)Cp,
-        stride[0], stride[1], stride[2], stride[3]);
-  } else {
-    tb200::pack_weights_krsc_kernel<uint32_t><<<blocks, threads, 0, stream>>>(
-        static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), total, (int)C, (int)R, (int)S, (int)S, (int)Cp,
-        stride[0], stride[1], stride[2], stride[3]);
-  }
-  TB_CUDA(cudaGetLastError());
-  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
-}
-
 void conv2d_prepack_checked(const TraceaTensorView& wv, void* dst, uint64_t dst_bytes, uint64_t* packed_shape,
                             int64_t* packed_stride, void* stream) {
   if (wv.ptr == nullptr || dst == nullptr || packed_shape == nullptr || packed_stride == nullptr)
@@ -1467,7 +1447,7 @@ void conv2d_prepack_checked(const TraceaTensorView& wv, void* dst, uint64_t dst_
   if (dst_bytes < need) TB_FAIL(TRACEA_INVALID_PARAMS, "dst holds %llu bytes, the packed weights need %llu",
                                 (unsigned long long)dst_bytes, need);
   DeviceGuard guard(w.device);
-  launch_weight_pack(w.ptr, dst, es, K, C, R, S, Cp, w.stride, static_cast<cudaStream_t>(stream));
+  launch_weight_pack(w.ptr, dst, es, K, C, R, S, S, Cp, w.stride, static_cast<cudaStream_t>(stream));
   packed_shape[0] = (uint64_t)K; packed_shape[1] = (uint64_t)Cp; packed_shape[2] = (uint64_t)R; packed_shape[3] = (uint64_t)S;
   packed_stride[0] = R * S * Cp; packed_stride[1] = 1; packed_stride[2] = S * Cp; packed_stride[3] = Cp;
 }
@@ -1488,7 +1468,7 @@ void gemm_prepack_b_checked(const TraceaTensorView& bv, void* dst, uint64_t dst_
                                 (unsigned long long)dst_bytes, need);
   DeviceGuard guard(bv.device_id);
   const long long stride[4] = {b.stride[1], b.stride[0], 0, 0};   // filter bank [N, K, 1, 1]
-  launch_weight_pack(bv.ptr, dst, es, N, K, 1, 1, K, stride, static_cast<cudaStream_t>(stream));
+  launch_weight_pack(bv.ptr, dst, es, N, K, 1, 1, 1, K, stride, static_cast<cudaStream_t>(stream));
   packed_stride[0] = 1;
   packed_stride[1] = K;
 }
