@@ -280,13 +280,9 @@ __device__ __forceinline__ void add16(float* f, const uint4& raw) {
 // strides, K_out not a multiple of the vector width): finishes one 32-column block of one pixel --
 // residual, activation, store. `f` holds accumulator + bias. Kept out of line so that the common
 // path's instruction footprint stays small.
-// `stg` is 4 KB of this warp's shared staging memory. Channel-contiguous, 16-byte-aligned outputs (a strided view,
-// one phase of a transposed convolution) are written through it: every lane parks its pixel's 32 columns there, then
-// the warp stores them with kRowChunks lanes per pixel, so that each store instruction covers whole 64- or 128-byte
-// rows instead of 32 scattered 16-byte pieces.
 template <typename OutT>
 __device__ __noinline__ void epilogue_block_generic(const ConvKernelArgs& args, float* f, const OutT* res_px,
-                                                    OutT* out_px, int n_first, bool row_ok, uint32_t stg, int lane) {
+                                                    OutT* out_px, int n_first, bool row_ok) {
   constexpr int kVec = 16 / sizeof(OutT);
   if (res_px != nullptr && row_ok) {
     if (args.res_vec) {
@@ -300,36 +296,17 @@ __device__ __noinline__ void epilogue_block_generic(const ConvKernelArgs& args, 
     }
   }
   apply_act32<sizeof(OutT) == 2>(*reinterpret_cast<float(*)[32]>(f), args.act);
-  if (args.out_vec) {   // warp-uniform
-    constexpr int kRowChunks = 32 / kVec;            // 16-byte chunks per pixel: 4 (16-bit) or 8 (fp32)
-    constexpr int kRowBytes = kRowChunks * 16;
-    constexpr int kRowsPerStep = 32 / kRowChunks;
-    const uint32_t my_row = stg + static_cast<uint32_t>(lane) * kRowBytes;
-#pragma unroll
-    for (int c = 0; c < kRowChunks; ++c)
-      ptx::st_shared_v4(my_row + ((static_cast<uint32_t>(c) ^ (static_cast<uint32_t>(lane) & (kRowChunks - 1))) << 4),
-                        pack16<OutT>(f + c * kVec));
-    __syncwarp();
-    const uint32_t ok_rows = __ballot_sync(0xffffffffu, row_ok);
-    const uint32_t chunk = static_cast<uint32_t>(lane) & (kRowChunks - 1);
-    const bool chunk_ok = n_first + static_cast<int>(chunk) * kVec < args.K_out;
-    const unsigned long long my_px = reinterpret_cast<unsigned long long>(out_px);
-#pragma unroll
-    for (int i = 0; i < kRowChunks; ++i) {
-      const int r = i * kRowsPerStep + lane / kRowChunks;
-      const unsigned long long px = __shfl_sync(0xffffffffu, my_px, r);
-      const uint4 v = ptx::ld_shared_v4(stg + static_cast<uint32_t>(r) * kRowBytes +
-                                        ((chunk ^ (static_cast<uint32_t>(r) & (kRowChunks - 1))) << 4));
-      if (chunk_ok && ((ok_rows >> r) & 1u)) reinterpret_cast<uint4*>(px)[chunk] = v;
-    }
-    __syncwarp();   // the staging rows are rewritten by the next block
-    return;
-  }
   if (!row_ok) return;
-  // lanes are consecutive pixels: for NCHW memory (sw == 1) each store instruction is coalesced
+  if (args.out_vec) {
+#pragma unroll
+    for (int c = 0; c < 32 / kVec; ++c)
+      if (n_first + c * kVec < args.K_out) reinterpret_cast<uint4*>(out_px)[c] = pack16<OutT>(f + c * kVec);
+  } else {
+    // lanes are consecutive pixels: for NCHW memory (sw == 1) each store instruction is coalesced
 #pragma unroll 4
-  for (int j = 0; j < 32; ++j)
-    if (n_first + j < args.K_out) out_px[j * args.out_sc] = OutTraits<OutT>::from_f(f[j]);
+    for (int j = 0; j < 32; ++j)
+      if (n_first + j < args.K_out) out_px[j * args.out_sc] = OutTraits<OutT>::from_f(f[j]);
+  }
 }
 
 // kPair: launched as clusters of two CTAs (cta_group::2). The pair owns a 256 x BN tile: each CTA loads its own
@@ -338,7 +315,48 @@ __device__ __noinline__ void epilogue_block_generic(const ConvKernelArgs& args, 
 // kRows2 (single CTA, narrow outputs): the CTA owns a 256 x BN tile as two 128-row blocks with one accumulator
 // each; a stage carries both A blocks and one B, i.e. eight MMAs per barrier probe instead of four, and the two
 // epilogue groups drain the two halves of the same tile instead of alternate tiles.
-template <typename OutT, int BN, bool kPair, bool kRows2>
+// Staging box (32 pixel rows x 128 bytes, SWIZZLE_128B layout: 16-byte chunk c of row r at r*128 + ((c ^ (r & 7)) << 4))
+// <-> global memory, moved by the warp itself for outputs the TMA unit cannot address as one matrix. Lane l handles
+// chunk l & 7 of rows (l >> 3) + 4 i, so each instruction covers four whole 128-byte rows. `row_base` points at the
+// first element of the group's columns in pixel 0's row; `row_off` is this lane's own pixel offset (in elements),
+// `row_ok` whether its pixel exists; `cols_left` = K_out - first column of the group. Only instantiated in the kCoop kernels.
+template <typename OutT>
+__device__ __noinline__ void coop_store_box(uint32_t stg, OutT* row_base, long long row_off, bool row_ok, int cols_left,
+                                            int lane) {
+  constexpr int kVec = 16 / sizeof(OutT);
+  __syncwarp();   // every lane's row is in the box
+  const uint32_t ok_rows = __ballot_sync(0xffffffffu, row_ok);
+  const uint32_t chunk = static_cast<uint32_t>(lane) & 7u;
+  const bool chunk_ok = static_cast<int>(chunk) * kVec < cols_left;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    const long long off = __shfl_sync(0xffffffffu, row_off, r);
+    const uint4 v = ptx::ld_shared_v4(stg + static_cast<uint32_t>(r) * 128u + ((chunk ^ (static_cast<uint32_t>(r) & 7u)) << 4));
+    if (chunk_ok && ((ok_rows >> r) & 1u)) *(reinterpret_cast<uint4*>(row_base + off) + chunk) = v;
+  }
+  __syncwarp();   // the box may be rewritten once every lane has read it out
+}
+
+template <typename OutT>
+__device__ __noinline__ void coop_load_box(uint32_t stg, const OutT* row_base, long long row_off, bool row_ok,
+                                           int cols_left, int lane) {
+  constexpr int kVec = 16 / sizeof(OutT);
+  const uint32_t ok_rows = __ballot_sync(0xffffffffu, row_ok);
+  const uint32_t chunk = static_cast<uint32_t>(lane) & 7u;
+  const bool chunk_ok = static_cast<int>(chunk) * kVec < cols_left;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    const long long off = __shfl_sync(0xffffffffu, row_off, r);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (chunk_ok && ((ok_rows >> r) & 1u)) v = __ldg(reinterpret_cast<const uint4*>(row_base + off) + chunk);
+    ptx::st_shared_v4(stg + static_cast<uint32_t>(r) * 128u + ((chunk ^ (static_cast<uint32_t>(r) & 7u)) << 4), v);
+  }
+  __syncwarp();   // rows were written by other lanes than the ones that read them next
+}
+
+template <typename OutT, int BN, bool kPair, bool kRows2, bool kCoop>
 __global__ void __launch_bounds__(kNumThreads, 1)
 conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ CUtensorMap tmap_w,
@@ -764,6 +782,12 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     (void)prof_wacc; (void)prof_wres; (void)prof_ld; (void)prof_math; (void)prof_stage; (void)prof_wstore;
     TB200_PROF_T(prof_t0);
     const bool need_coords = !args.out_tma || (res != nullptr && !res_tma);
+    // kCoop kernels serve channel-contiguous outputs whose pixels are not one dense [M][pitch] matrix (a strided
+    // view, one phase of a transposed convolution; the host launches them only then, with out_tma = 0): same staging
+    // boxes as the TMA path, but the warp moves them itself, 8 lanes per pixel and 16 bytes each, so every store /
+    // residual load instruction covers 4 whole 128-byte rows. A separate instantiation, because inside the TMA
+    // kernels this code cost 1.3 % through register spills.
+    const bool res_staged = res_tma || (kCoop && res != nullptr);
     for (int tile = etile0; tile < num_tiles && ok; tile += estride, local_tile += (kRows2 ? 1 : 2)) {
       tile_coords(tile, m_tile, n_tile);
       const int buf = kRows2 ? (local_tile & 1) : egroup;
@@ -872,6 +896,9 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           __syncwarp();
           TB200_PROF_ADD(prof_wstore, ts);
         }
+        if constexpr (kCoop) {
+          if (res != nullptr) coop_load_box<OutT>(stg, res + n0, res_off, row_ok, args.K_out - n0, lane);
+        }
 
         TB200_PROF_T(tm);
         uint4 packed[8];
@@ -886,19 +913,19 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             add2(f[j4 * 4 + 0], f[j4 * 4 + 1], b4.x, b4.y);
             add2(f[j4 * 4 + 2], f[j4 * 4 + 3], b4.z, b4.w);
           }
-          if (!args.out_tma) {
+          if (!kCoop && !args.out_tma) {
             float fg[32];   // a copy the out-of-line path may keep in local memory; f stays in registers
 #pragma unroll
             for (int j = 0; j < 32; ++j) fg[j] = f[j];
             epilogue_block_generic<OutT>(
                 args, fg, res != nullptr ? res_row + static_cast<long long>(g * kGroupCols + h * 32) * args.res_sc : nullptr,
-                out + out_off + static_cast<long long>(n0 + h * 32) * args.out_sc, n0 + h * 32, row_ok, stg, lane);
+                out + out_off + static_cast<long long>(n0 + h * 32) * args.out_sc, n0 + h * 32, row_ok);
             continue;
           }
           // TMA output; a residual, if any, sits in this lane's row of the staging box (the host
           // guarantees a residual is TMA-loaded whenever the output is TMA-stored)
           uint4 rchunks[kChunksPerLd];
-          if (res_tma) {
+          if (res_staged) {
 #pragma unroll
             for (int c = 0; c < kChunksPerLd; ++c) {
               const uint32_t cc = static_cast<uint32_t>(h * kChunksPerLd + c);
@@ -906,9 +933,9 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             }
           }
           if (args.act == kActRelu) {
-            finish32<OutT, true>(f, rchunks, res_tma, packed + h * kChunksPerLd);
+            finish32<OutT, true>(f, rchunks, res_staged, packed + h * kChunksPerLd);
           } else {
-            if (res_tma) {
+            if (res_staged) {
 #pragma unroll
               for (int c = 0; c < kChunksPerLd; ++c) add16<OutT>(f + c * kVec, rchunks[c]);
             }
@@ -929,6 +956,12 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             tma_store_2d(&tmap_out, stg, n0, m_row0);
             bulk_commit_group();
           }
+          box ^= 1u;
+        } else if constexpr (kCoop) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            st_shared_v4(stg + lane_row_off + ((static_cast<uint32_t>(c) ^ lane_xor) << 4), packed[c]);
+          coop_store_box<OutT>(stg, out + n0, out_off, row_ok, args.K_out - n0, lane);
           box ^= 1u;
         }
         TB200_PROF_ADD(prof_stage, tg);

@@ -74,7 +74,7 @@ struct DeviceState {
   int num_sms = 0;
   cudaMemPool_t pool = nullptr;
   uint32_t* status = nullptr;  // pinned, mapped: kernels write error codes the host reads directly
-  bool attr_set[3][3][3] = {};   // [dtype][bn index][tiling: single CTA / CTA pair / two row blocks]
+  bool attr_set[3][3][6] = {};   // [dtype][bn index][tiling: single CTA / CTA pair / two row blocks, x2 for the coop epilogue]
   // host-memory path only: copy streams and events for the chunked H2D / compute / D2H pipeline
   static constexpr int kMaxChunks = 16;
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -303,12 +303,12 @@ int pick_stages(int bn, bool pair, bool rows2, bool shared_bias) {
   return std::min(s, tb200::kMaxStages);
 }
 
-template <typename OutT, int BN, bool kPair, bool kRows2 = false>
+template <typename OutT, int BN, bool kPair, bool kRows2, bool kCoop>
 void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, const CUtensorMap& tw,
                 const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid, int smem,
                 cudaStream_t stream) {
-  auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN, kPair, kRows2>;
-  constexpr int kVariant = kPair ? 1 : (kRows2 ? 2 : 0);
+  auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN, kPair, kRows2, kCoop>;
+  constexpr int kVariant = (kPair ? 1 : (kRows2 ? 2 : 0)) + (kCoop ? 3 : 0);
   if (!st.attr_set[dt_idx][bn_idx][kVariant]) {
     TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     st.attr_set[dt_idx][bn_idx][kVariant] = true;
@@ -335,25 +335,34 @@ void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, 
   g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
-template <typename OutT>
-void launch_bn(DeviceState& st, int dt_idx, int bn, bool pair, bool rows2, const CUtensorMap& tx,
-               const CUtensorMap& tw, const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid,
-               int smem, cudaStream_t stream) {
+// `coop`: the kernel variant whose epilogue moves its staging boxes to a strided, channel-contiguous output itself.
+template <typename OutT, bool kCoop>
+void launch_tiling(DeviceState& st, int dt_idx, int bn, bool pair, bool rows2, const CUtensorMap& tx,
+                   const CUtensorMap& tw, const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args,
+                   int grid, int smem, cudaStream_t stream) {
   if (rows2) {
-    if (bn == 64) launch_one<OutT, 64, false, true>(st, dt_idx, 0, tx, tw, to, tr, args, grid, smem, stream);
-    else launch_one<OutT, 128, false, true>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream);
+    if (bn == 64) launch_one<OutT, 64, false, true, kCoop>(st, dt_idx, 0, tx, tw, to, tr, args, grid, smem, stream);
+    else launch_one<OutT, 128, false, true, kCoop>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream);
     return;
   }
   if (pair) {
-    if (bn == 128) launch_one<OutT, 128, true>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream);
-    else launch_one<OutT, 256, true>(st, dt_idx, 2, tx, tw, to, tr, args, grid, smem, stream);
+    if (bn == 128) launch_one<OutT, 128, true, false, kCoop>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream);
+    else launch_one<OutT, 256, true, false, kCoop>(st, dt_idx, 2, tx, tw, to, tr, args, grid, smem, stream);
     return;
   }
   switch (bn) {
-    case 64: launch_one<OutT, 64, false>(st, dt_idx, 0, tx, tw, to, tr, args, grid, smem, stream); break;
-    case 128: launch_one<OutT, 128, false>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream); break;
-    default: launch_one<OutT, 256, false>(st, dt_idx, 2, tx, tw, to, tr, args, grid, smem, stream); break;
+    case 64: launch_one<OutT, 64, false, false, kCoop>(st, dt_idx, 0, tx, tw, to, tr, args, grid, smem, stream); break;
+    case 128: launch_one<OutT, 128, false, false, kCoop>(st, dt_idx, 1, tx, tw, to, tr, args, grid, smem, stream); break;
+    default: launch_one<OutT, 256, false, false, kCoop>(st, dt_idx, 2, tx, tw, to, tr, args, grid, smem, stream); break;
   }
+}
+
+template <typename OutT>
+void launch_bn(DeviceState& st, int dt_idx, int bn, bool pair, bool rows2, bool coop, const CUtensorMap& tx,
+               const CUtensorMap& tw, const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid,
+               int smem, cudaStream_t stream) {
+  if (coop) launch_tiling<OutT, true>(st, dt_idx, bn, pair, rows2, tx, tw, to, tr, args, grid, smem, stream);
+  else launch_tiling<OutT, false>(st, dt_idx, bn, pair, rows2, tx, tw, to, tr, args, grid, smem, stream);
 }
 
 CUtensorMapDataType tmap_dtype(TraceaDType t) {
@@ -424,7 +433,7 @@ struct NoAllocState {
   bool ready = false;
   int num_sms = 0;
   unsigned char* scratch = nullptr;   // device address of g_static_scratch on this device
-  bool attr_set[3][3][3] = {};
+  bool attr_set[3][3][6] = {};
 };
 NoAllocState g_noalloc[kMaxDevices];
 
@@ -848,6 +857,9 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   }
   a.act = epi.act;
   a.status = st.status;
+  // channel-contiguous output (and residual, if any) that the TMA unit cannot address as one matrix: the kernel
+  // variant whose epilogue writes its staging boxes out itself, whole 128-byte rows at a time
+  const bool coop = !a.out_tma && a.out_vec && (a.residual == nullptr || a.res_vec);
 #ifdef TB200_PROFILE
   {  // bring-up builds only: TRACEA_B200_PROF_PTR carries a device pointer to 8 counters per CTA
     const char* pp = getenv("TRACEA_B200_PROF_PTR");
@@ -905,13 +917,13 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
                             : static_cast<int>(std::min<long long>(tiles, st.num_sms));
     switch (x.dtype) {
       case TRACEA_DTYPE_BFLOAT16:
-        launch_bn<__nv_bfloat16>(st, 0, bn, pair_v, rows2_v, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
+        launch_bn<__nv_bfloat16>(st, 0, bn, pair_v, rows2_v, coop, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
         break;
       case TRACEA_DTYPE_FLOAT16:
-        launch_bn<__half>(st, 1, bn, pair_v, rows2_v, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
+        launch_bn<__half>(st, 1, bn, pair_v, rows2_v, coop, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
         break;
       default:
-        launch_bn<float>(st, 2, bn, pair_v, rows2_v, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
+        launch_bn<float>(st, 2, bn, pair_v, rows2_v, coop, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
         break;
     }
   };
