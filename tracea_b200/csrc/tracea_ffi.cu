@@ -276,12 +276,14 @@ Epilogue decode_epilogue(TraceaEpilogueKind kind, bool have_bias, bool have_res)
 }
 
 // ------------------------------------------------------------------ tile selection
-// Relative cost of one 128-byte k-step of a 128 x BN tile on one SM: the larger of the tensor
-// pipe time (BN/2 cycles per MMA) and the shared-memory operand read time
-// ((128 + BN) * 32 B per MMA at 128 B/cycle). The widest tile wins ties: it re-reads A least.
+// Relative cost of one 128-byte k-step of a 128-row x BN tile on one SM, measured on the ResNet-50 layers rather
+// than derived: the tensor pipe alone would give 512 / 256 / 192 cycles (BN/2 per MMA, 48 at BN = 64 where the
+// shared-memory operand reads bind), but the narrower tiles pull (128 + BN) * 128 bytes per step through L2 -> SM
+// paths that deliver ~70 B/cycle/SM when every SM loads, so a BN = 128 step costs ~400 and a BN = 64 step ~300.
+// The widest tile wins ties: it re-reads A least.
 int pick_bn(long long m_tiles, int k_out, int num_sms) {
   const int bns[3] = {256, 128, 64};
-  const int step_cost[3] = {512, 256, 192};
+  const int step_cost[3] = {512, 400, 300};
   long long best_cost = -1;
   int best = 64;
   for (int i = 0; i < 3; ++i) {
@@ -772,10 +774,14 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   a.C = static_cast<int>(Cg);
   a.a_tiled = a_tiled ? 1 : 0;
   // L2 prefetch of the activations a few k-steps ahead of the loads: pays only where A streams from HBM with
-  // no reuse and the k-loop is long (1x1 layers with >= 8 k-steps: -3 %); it slows 3x3 layers down (their A
-  // mostly hits L2 already). TRACEA_B200_PREFETCH=n forces a distance, -1 switches it off.
+  // no reuse and the k-loop is long (1x1 layers with >= 8 k-steps, one column tile, at least two waves: -3 %);
+  // it slows down 3x3 layers and layers whose A is re-read by several column tiles (their A mostly hits L2
+  // already). TRACEA_B200_PREFETCH=n forces a distance, -1 switches it off.
   a.prefetch_dist = knobs().prefetch > 0 ? knobs().prefetch
-                    : (knobs().prefetch == 0 && R == 1 && S == 1 && total_chunks_ll >= 8 ? 4 : 0);
+                    : (knobs().prefetch == 0 && R == 1 && S == 1 && total_chunks_ll >= 8 && n_tiles == 1 &&
+                               m_tiles_128 >= 2LL * st.num_sms
+                           ? 4
+                           : 0);
   a.num_n_tiles = static_cast<int>(n_tiles);
   a.b_k0 = static_cast<int>(b_k0);
   a.b_jump_s = static_cast<int>(b_jump_s);
