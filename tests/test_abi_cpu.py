@@ -213,7 +213,10 @@ def test_last_error_is_thread_local(lib):
     assert seen["msg"] == "" and ffi.last_error() == "Unsupported groups: 2"
 
 
-REF_HPP = "/root/reference/include/tracea.hpp"
+# the reference checkout, when present, sits next to this repository (or where TRACEA_REFERENCE_ROOT points)
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_HPP = os.path.join(os.environ.get("TRACEA_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference")),
+                       "include", "tracea.hpp")
 
 
 @pytest.mark.skipif(not os.path.exists(REF_HPP) or shutil.which("g++") is None,
