@@ -236,13 +236,33 @@ int main() {
   tracea::Conv2dParams p;
   p.padding_h = p.padding_w = 1;
   p.groups = 2;  // rejected by validation, with or without a GPU
+  int caught = 0;
   try {
     tracea::conv2d(tx, tw, nullptr, nullptr, to, p);
   } catch (const std::runtime_error& e) {
     std::printf("%s\n", e.what());
-    return 0;
+    ++caught;
   }
-  return 1;
+  // the GEMM and ConvTranspose2d wrappers of the same header resolve against this library too
+  std::vector<float> a(4 * 8), b(7 * 6), c(4 * 6);
+  tracea::TensorView ta(a.data(), {4, 8}, tracea::DType::Float32);
+  tracea::TensorView tb(b.data(), {7, 6}, tracea::DType::Float32);     // inner dimension mismatch
+  tracea::TensorView tc(c.data(), {4, 6}, tracea::DType::Float32);
+  try {
+    tracea::gemm(ta, tb, nullptr, nullptr, tc, tracea::GemmParams());
+  } catch (const std::runtime_error& e) {
+    std::printf("%s\n", e.what());
+    ++caught;
+  }
+  tracea::ConvTranspose2dParams tp;
+  tp.groups = 2;
+  try {
+    tracea::conv_transpose2d(tx, tw, nullptr, nullptr, to, tp);
+  } catch (const std::runtime_error& e) {
+    std::printf("%s\n", e.what());
+    ++caught;
+  }
+  return caught == 3 ? 0 : 1;
 }
 ''')
     exe = tmp_path / "caller"
@@ -251,4 +271,8 @@ int main() {
                     "-L", libdir, "-ltracea_b200", "-Wl,-rpath," + libdir, "-Wl,--allow-shlib-undefined"], check=True)
     res = subprocess.run([str(exe)], capture_output=True, text=True)
     assert res.returncode == 0
-    assert res.stdout.strip() == "tracea::conv2d failed: Unsupported groups: 2"
+    assert res.stdout.strip().splitlines() == [
+        "tracea::conv2d failed: Unsupported groups: 2",
+        "tracea::gemm failed: Inner dimension mismatch: a is [4,8], b is [7,6]",
+        "tracea::conv_transpose2d failed: Unsupported groups: 2",
+    ]
