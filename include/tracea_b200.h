@@ -100,10 +100,18 @@ typedef struct {
   void *stream;
 } TraceaConv2dParamsV0;
 
-/* out = epilogue(conv2d(x, w)). Replaces include/tracea.hpp:107-110 and the in-crate entry
- * src/interface/c_bindings.rs:205-290. Validation mirrors tracea-ffi/src/lib.rs:150-207:
+/* out = epilogue(conv2d(x, w)). Replaces include/tracea.hpp:107-110 (the tracea-ffi entry,
+ * tracea-ffi/src/lib.rs:121-207). Validation mirrors tracea-ffi/src/lib.rs:150-207:
  * NULL x.ptr / w.ptr / out -> INVALID_PARAMS; rank != 4 -> INVALID_PARAMS; groups != 1 ->
- * UNSUPPORTED_CONFIG; zero stride or an `out` shape that is not [N,K,Ho,Wo] -> INVALID_PARAMS. */
+ * UNSUPPORTED_CONFIG; zero stride or an `out` shape that is not [N,K,Ho,Wo] -> INVALID_PARAMS.
+ *
+ * Shape order: `shape` is logical [N,C,H,W] for x / out / residual and [K,C,R,S] for w, as tracea.hpp
+ * documents and tracea-ffi reads them; the strides say how that sits in memory. The reference's OTHER conv2d
+ * entry of the same name, the in-crate src/interface/c_bindings.rs:205-290, reads x.shape as [N,H,W,C] and
+ * w.shape as [K,R,S,C]: a caller of that entry must permute its shape (and stride) arrays to [N,C,H,W] /
+ * [K,C,R,S] when it moves to this library -- the call still links unchanged, and a shape check cannot tell
+ * the two orders apart when the extents happen to agree. tracea_conv_transpose2d below does take the
+ * [N,H,W,C] / [K,R,S,C] order, because the in-crate entry is the only one the reference has for it. */
 TraceaStatus tracea_conv2d(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView *b,
                            const TraceaTensorView *residual, TraceaTensorView *out,
                            TraceaConv2dParams params);
@@ -138,6 +146,9 @@ TraceaStatus tracea_conv2d_v0(TraceaTensorView x, TraceaTensorView w, const Trac
  *     can overlap on the GPU (different streams, no ordering between them) race on it. Order such
  *     calls with events or keep them on one stream.
  *   - The array is resident on every GPU that loads the library, until the process exits.
+ *   - A kernel that gives up a bounded wait records its code in status words that also live in the device
+ *     image (not in pinned host memory, which would have to be allocated). Unlike tracea_conv2d, this entry
+ *     therefore does not look at them on the way in; tracea_b200_device_status copies them back and clears them.
  * Arguments, epilogue rules, validation and status codes are those of tracea_conv2d. */
 TraceaStatus tracea_conv2d_noalloc(TraceaTensorView x, TraceaTensorView w, const TraceaTensorView *b,
                                    const TraceaTensorView *residual, TraceaTensorView *out,
@@ -235,11 +246,19 @@ uint32_t tracea_version_patch(void);
 int tracea_init(void);
 void tracea_shutdown(void);
 
-/* Reads and clears the device-side status word of `device_id`: 0 when every conv kernel launched
+/* Reads and clears the device-side status words of `device_id`: 0 when every conv kernel launched
  * so far on that device finished normally, otherwise the code of the first bounded wait that ran
- * out inside a kernel (see conv2d_sm100.cuh). Call after synchronising the stream. The reference
+ * out inside a kernel (see conv2d_sm100.cuh). Covers both the kernels of tracea_conv2d (words in pinned host
+ * memory) and those of tracea_conv2d_noalloc (words in device memory, fetched with a blocking copy once that
+ * entry has been used on the device). Call after synchronising the stream. The reference
  * has no counterpart: its kernels spin without limit. */
 uint32_t tracea_b200_device_status(int32_t device_id);
+
+/* Byte counters of the library's stream-ordered scratch pool on `device_id`:
+ * stats = {reserved now, reserved high-water mark, in use now, in-use high-water mark}; reset_high != 0 resets
+ * the two high-water marks after reading. Returns 1, 0 when the device has no pool yet (stats all zero), -1 on
+ * bad arguments. Lets a test show that a call took nothing from the pool. No counterpart in the reference. */
+int32_t tracea_b200_pool_stats(int32_t device_id, uint64_t stats[4], int32_t reset_high);
 
 /* Number of GPU kernels this library has launched in this process so far (conv kernels and layout adapters;
  * a call may launch more than one: a layout adapter per staged operand, one conv launch per phase of a transposed

@@ -213,6 +213,74 @@ def test_config5_resnet50_conv_stack_n2_every_layer():
         assert cc.rel_err(got, cc.round_to(np.ascontiguousarray(want), "bf16")) <= cc.TOL_16BIT, sp.name
 
 
+def _sampled_layer_check(stack, sp, images, points, rng):
+    """One layer of a resident conv stack against fp64 dot products over its actual (GPU-produced) input, on
+    `points` output points spread over the images `images` (a convolution never mixes images, so the sub-batch is
+    checked as a batch of its own)."""
+    sel = torch.as_tensor(images, device="cuda")
+    src = stack.tensors[sp.src].index_select(0, sel).float().cpu().numpy()
+    got = stack.tensors[sp.dst].index_select(0, sel).float().cpu().numpy()
+    res = stack.tensors[sp.res].index_select(0, sel).float().cpu().numpy() if sp.res is not None else None
+    w = stack.weights[sp.name].float().cpu().numpy()
+    b = stack.biases[sp.name].cpu().numpy()
+    _, _, act = split_epi(sp.epilogue)
+    idx = np.stack([rng.integers(0, s, points) for s in got.shape], axis=1)
+    want = oracle.conv2d_points(src, w, idx, b, res, sp.stride, sp.pad, 1, act, acc_double=True)
+    vals = got[idx[:, 0], idx[:, 1], idx[:, 2], idx[:, 3]]
+    assert np.abs(vals - want).max() <= cc.TOL_16BIT * np.abs(want).max(), sp.name
+
+
+@pytest.mark.parametrize("n", [64, 512])
+def test_config5_resnet50_conv_stack_at_the_benchmark_batches(n):
+    """The 53 convs at the per-GPU batches the benchmark times them at (512 on one GPU, 64 on each of eight):
+    here every layer runs its multi-wave, panelled, CTA-pair and split tilings. Each layer: 2*10^4 output points
+    over eight images (the first, the last, six in between) against the oracle on the layer's own input; and
+    images 0..1 of every tensor against the N=2 run of the same stack (the ResNet-50 layer shapes of
+    src/optimizer/benchmark.rs:474-509 at full batch)."""
+    img, pooled = _stack_inputs(8)
+    reps = (n + 7) // 8
+    specs = resnet50.resnet50_convs()
+
+    def make(count):
+        ti = to_dev(img, "bf16").repeat(reps, 1, 1, 1)[:count].contiguous(memory_format=torch.channels_last)
+        tp = to_dev(pooled, "bf16").repeat(reps, 1, 1, 1)[:count].contiguous(memory_format=torch.channels_last)
+        # images differ across the batch: scale image i by a power of two (exact in bf16)
+        scale = (2.0 ** (torch.arange(count, device="cuda") % 3 - 1)).to(torch.bfloat16).view(-1, 1, 1, 1)
+        cl = lambda t: t.contiguous(memory_format=torch.channels_last)
+        return runner.ConvStack(specs, count, "bf16", "cuda", seed=5,
+                                inputs={"image": cl(ti * scale), "pooled": cl(tp * scale)})
+
+    stack = make(n)
+    stack.forward()
+    torch.cuda.synchronize()
+    assert ffi.load().tracea_b200_device_status(0) == 0
+    rng = np.random.default_rng(50 + n)
+    for sp in specs:
+        images = sorted({0, n - 1, *rng.integers(1, n - 1, 6).tolist()})
+        _sampled_layer_check(stack, sp, images, 20000, rng)
+    small = make(2)
+    small.forward()
+    torch.cuda.synchronize()
+    for sp in specs:
+        a, b = stack.tensors[sp.dst][:2].float(), small.tensors[sp.dst].float()
+        # identical inputs, possibly different tilings (a long-K layer of a small batch may be split over K, which
+        # changes the fp32 summation order): results agree to the last bf16 place
+        scale = float(b.abs().max())
+        assert float((a - b).abs().max()) <= 2.0 ** -7 * scale, sp.name
+        assert float((a != b).float().mean()) <= 2e-2, sp.name
+
+
+def test_config3_c2_n256_full_tensor_against_the_oracle():
+    """The headline layer (3x3 256->256 at 256 images) compared in full: all 12.8 M outputs against the oracle's
+    im2col + GEMM path on the layer's actual bf16 input."""
+    x, ws, bs = _block_inputs(256)
+    stack = _block_gpu(x, ws, bs)
+    y1 = stack.tensors["block.c1"].float().cpu().numpy()
+    want = oracle.conv2d_gemm(cc.channels_last(y1), cc.round_to(ws[1], "bf16"), bs[1], None, 1, 1, 1, "relu")
+    got = stack.tensors["block.c2"].float().cpu().numpy()
+    assert cc.rel_err(got, cc.round_to(np.ascontiguousarray(want), "bf16")) <= cc.TOL_16BIT
+
+
 # --------------------------------------------------------------------------- size-independent properties
 def test_identity_filter_reproduces_the_input_bit_exactly_at_full_size():
     """A 1x1 filter that is the identity matrix copies x to out exactly (x*1 + 0*... in fp32 is

@@ -12,6 +12,7 @@ import pytest
 import torch
 
 import convcases as cc
+from oracle import oracle
 from tracea_b200 import ffi, ops
 
 pytestmark = pytest.mark.gpu
@@ -30,33 +31,71 @@ CASES = [
     ("f32", 1, 64, 56, 56, 64, 3, 1, 1, "bias+relu"),
     ("bf16", 3, 24, 17, 19, 40, 3, 2, 1, "bias+residual+relu"),
 ]
+DT = {"f32": torch.float32, "bf16": torch.bfloat16}
 
 
-def test_noalloc_entry_matches_tracea_conv2d_on_two_calls_in_a_row():
-    dt = {"f32": torch.float32, "bf16": torch.bfloat16}
-    for dtype, N, C, H, W, K, R, stride, pad, epi in CASES:        # two different calls back to back
-        x = torch.from_numpy(cc.uniform((N, C, H, W), 11, "na/x")).to(dt[dtype]).cuda()
-        w = torch.from_numpy(cc.kaiming((K, C, R, R), 11, "na/w")).to(dt[dtype]).cuda()
-        b = torch.from_numpy(cc.normal((K,), 11, "na/b", 0.1)).cuda()
-        ho, wo = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - R) // stride + 1
-        res = torch.from_numpy(cc.normal((N, K, ho, wo), 11, "na/r")).to(dt[dtype]).cuda() if "residual" in epi else None
-        kind = ops.parse_epilogue(epi, b, res)
-        want = _call("tracea_conv2d", x, w, b, res, torch.empty((N, K, ho, wo), dtype=dt[dtype], device="cuda"),
-                     stride, pad, kind)
-        got = _call("tracea_conv2d_noalloc", x, w, b, res,
-                    torch.full((N, K, ho, wo), float("nan"), dtype=dt[dtype], device="cuda"), stride, pad, kind)
-        err = cc.rel_err(got.float().cpu().numpy(), want.float().cpu().numpy())
+def _inputs(case, seed):
+    dtype, N, C, H, W, K, R, stride, pad, epi = case
+    x = cc.uniform((N, C, H, W), seed, "na/x")
+    w = cc.kaiming((K, C, R, R), seed, "na/w")
+    b = cc.normal((K,), seed, "na/b", 0.1)
+    ho, wo = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - R) // stride + 1
+    res = cc.normal((N, K, ho, wo), seed, "na/r") if "residual" in epi else None
+    return x, w, b, res, (N, K, ho, wo)
+
+
+def _oracle(case, x, w, b, res):
+    dtype, _, _, _, _, _, _, stride, pad, epi = case
+    xr, wr = cc.round_to(x, dtype), cc.round_to(w, dtype)
+    rr = cc.round_to(res, dtype) if res is not None else None
+    want = oracle.conv2d_gemm(cc.channels_last(xr), wr, b, rr, stride, pad, 1, "relu")
+    return cc.round_to(np.ascontiguousarray(want), dtype)
+
+
+def test_noalloc_entry_matches_tracea_conv2d_and_the_oracle_on_two_calls_in_a_row():
+    """Same kernel, same inputs: the two entries must agree bit for bit, and both with the CPU oracle."""
+    for seed, case in ((11, CASES[0]), (11, CASES[1]), (12, CASES[0])):   # the last: after the scratch held other data
+        dtype, _, _, _, _, _, _, stride, pad, epi = case
+        x, w, b, res, oshape = _inputs(case, seed)
+        tx, tw = torch.from_numpy(x).to(DT[dtype]).cuda(), torch.from_numpy(w).to(DT[dtype]).cuda()
+        tb = torch.from_numpy(b).cuda()
+        tr = torch.from_numpy(res).to(DT[dtype]).cuda() if res is not None else None
+        kind = ops.parse_epilogue(epi, tb, tr)
+        want = _call("tracea_conv2d", tx, tw, tb, tr, torch.empty(oshape, dtype=DT[dtype], device="cuda"), stride, pad,
+                     kind)
+        got = _call("tracea_conv2d_noalloc", tx, tw, tb, tr,
+                    torch.full(oshape, float("nan"), dtype=DT[dtype], device="cuda"), stride, pad, kind)
+        assert torch.equal(got, want), (dtype, seed)
+        err = cc.rel_err(got.float().cpu().numpy(), _oracle(case, x, w, b, res))
         assert err <= cc.tol_for(dtype), (dtype, err)
-    # and the first case once more, after the scratch has held another call's data
-    dtype, N, C, H, W, K, R, stride, pad, epi = CASES[0]
-    x = torch.from_numpy(cc.uniform((N, C, H, W), 12, "na/x")).cuda()
-    w = torch.from_numpy(cc.kaiming((K, C, R, R), 12, "na/w")).cuda()
-    b = torch.from_numpy(cc.normal((K,), 12, "na/b", 0.1)).cuda()
-    kind = ops.parse_epilogue(epi, b, None)
-    want = _call("tracea_conv2d", x, w, b, None, torch.empty((N, K, H, W), device="cuda"), stride, pad, kind)
-    got = _call("tracea_conv2d_noalloc", x, w, b, None, torch.empty((N, K, H, W), device="cuda"), stride, pad, kind)
-    assert cc.rel_err(got.cpu().numpy(), want.cpu().numpy()) <= cc.TOL_TF32
     assert ffi.load().tracea_b200_device_status(0) == 0
+
+
+def test_noalloc_entry_takes_no_memory_from_the_device_or_the_pool():
+    """Steady state (the kernels of this shape have run once, so the driver has loaded them): across a call
+    the device's free memory does not move and the library's scratch pool hands nothing out."""
+    case = CASES[0]
+    dtype, _, _, _, _, _, _, stride, pad, epi = case
+    x, w, b, res, oshape = _inputs(case, 13)
+    tx, tw, tb = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda()
+    out = torch.empty(oshape, device="cuda")
+    kind = ops.parse_epilogue(epi, tb, None)
+    _call("tracea_conv2d", tx, tw, tb, None, out, stride, pad, kind)          # brings the pool up
+    _call("tracea_conv2d_noalloc", tx, tw, tb, None, out, stride, pad, kind)  # one-time set-up, module loading
+    ffi.pool_stats(0, reset_high=True)
+    before = ffi.pool_stats(0)
+    assert before is not None
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        _call("tracea_conv2d_noalloc", tx, tw, tb, None, out, stride, pad, kind)
+    free_after, _ = torch.cuda.mem_get_info()
+    after = ffi.pool_stats(0)
+    assert free_after == free_before
+    assert after["used"] == before["used"] and after["reserved"] == before["reserved"]
+    assert after["used_high"] <= before["used"]          # nothing was handed out since the reset
+    # the allocating entry on the same inputs does go to the pool (the counter is live)
+    _call("tracea_conv2d", tx, tw, tb, None, out, stride, pad, kind)
+    assert ffi.pool_stats(0)["used_high"] > before["used"]
 
 
 def test_noalloc_entry_rejects_what_does_not_fit_and_host_memory():

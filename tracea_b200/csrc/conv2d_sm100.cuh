@@ -95,6 +95,9 @@ struct ConvKernelArgs {
   // error reporting: 4 words {code, block, detail, 0}; first error wins
   uint32_t* status;
   long long* prof;        // cycle counters, only written by -DTB200_PROFILE builds
+#ifdef TB200_ABLATE
+  int dbg;                // bring-up builds only: bit 0 no B loads, 1 no A loads, 2 every tile reads tile 0's A, 3 no MMAs, 4 no stores
+#endif
 };
 
 template <typename T> struct OutTraits;
@@ -543,6 +546,35 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             uint32_t nstage = stage_addr + kStageBytes, nfull = full_addr + 8u, nempty = empty_addr + 8u, nphase = phase;
             if (nstage == ring_end) { nstage = smem_base; nfull = full_bar0; nempty = empty_bar0; nphase ^= 1u; }
             bool next_free;
+#ifdef TB200_ABLATE
+            if constexpr (kPair) {
+              if (args.dbg & 7) {
+                const bool no_b = args.dbg & 1, no_a = args.dbg & 2;
+                const int img_a = (args.dbg & 4) ? 0 : img0;
+                const int w_a = (args.dbg & 4) ? (int)cta_rank * kBlockM * 0 - args.pad_w : w_start;
+                const int h_a = (args.dbg & 4) ? -args.pad_h : h_start;
+                const uint32_t bytes = (no_a ? 0u : kABytes) + (no_b ? 0u : kBBytes);
+                next_free = mbar_test_wait(nempty, nphase ^ 1u);
+                const uint32_t fl = full_leader0 + (full_addr - full_bar0);
+                if (leader) mbar_arrive_expect_tx(full_addr, 2u * bytes);
+                if (!no_a)
+                  asm volatile(
+                      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+                      " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(stage_addr),
+                      "l"(reinterpret_cast<uint64_t>(&tmap_x)), "r"(fl), "r"(c_coord), "r"(w_a), "r"(h_a), "r"(img_a),
+                      "h"((uint16_t)off_w), "h"((uint16_t)off_h)
+                      : "memory");
+                if (!no_b)
+                  asm volatile(
+                      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+                      " [%0], [%1, {%3, %4}], [%2];" ::"r"(stage_addr + kABytes),
+                      "l"(reinterpret_cast<uint64_t>(&tmap_w)), "r"(fl), "r"(k_coord), "r"(n_coord)
+                      : "memory");
+                if (bytes == 0u && leader) { /* nothing in flight: the expect_tx(0) arrive completes the phase */ }
+                goto stage_issued;
+              }
+            }
+#endif
             if constexpr (kPair) {
               // both CTAs' copies complete on the leader's full barrier; the leader arms it for both
               next_free = tma_stage_probe_pair(stage_addr, stage_addr + kABytes, full_addr,
@@ -559,6 +591,9 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                           w_start, h_start, img0, (uint16_t)off_w, (uint16_t)off_h, &tmap_w, k_coord,
                                           n_coord, nempty, nphase ^ 1u);
             }
+#ifdef TB200_ABLATE
+          stage_issued:
+#endif
             if (do_prefetch) pf_step();
             k_coord += args.chunk_elems;
             c_coord += args.chunk_elems;

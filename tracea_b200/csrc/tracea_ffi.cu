@@ -70,11 +70,12 @@ typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapFloatOOBfill);
 
 struct DeviceState {
-  bool ready = false;
+  std::atomic<bool> ready{false};
+  int dev = 0;
   int num_sms = 0;
   cudaMemPool_t pool = nullptr;
   uint32_t* status = nullptr;  // pinned, mapped: kernels write error codes the host reads directly
-  bool attr_set[3][3][6] = {};   // [dtype][bn index][tiling: single CTA / CTA pair / two row blocks, x2 for the coop epilogue]
+  std::mutex host_mu;          // one host-memory call at a time per device (it owns the copy streams below)
   // host-memory path only: copy streams and events for the chunked H2D / compute / D2H pipeline
   static constexpr int kMaxChunks = 16;
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -83,14 +84,22 @@ struct DeviceState {
 };
 
 constexpr int kMaxDevices = 64;
-std::mutex g_mutex;
-std::mutex g_host_path_mutex;   // one host-memory call at a time per process (it owns the copy streams)
+// Locking: each device's state is brought up once under its own mutex and is read-only afterwards, so host
+// threads that drive different GPUs (or the same GPU on different streams) do not serialise on the call path:
+// validation, tensor-map encoding and the launch itself run without any lock.
+std::mutex g_dev_mu[kMaxDevices];
+std::mutex g_driver_mu;
 DeviceState g_dev[kMaxDevices];
+// "opt-in shared memory size has been set for this kernel variant on this device":
+// [device][dtype][bn index][tiling: single CTA / CTA pair / two row blocks, x2 for the coop epilogue].
+// Setting the attribute twice is harmless, so a relaxed flag is enough.
+std::atomic<bool> g_attr_set[kMaxDevices][3][3][6];
 std::atomic<unsigned long long> g_kernel_launches{0};   // every kernel this library has launched (conv + layout adapters)
 EncodeTiledFn g_encode_tiled = nullptr;
 EncodeIm2colFn g_encode_im2col = nullptr;
 
 void load_driver_entry_points() {
+  std::lock_guard<std::mutex> lock(g_driver_mu);
   if (g_encode_tiled != nullptr && g_encode_im2col != nullptr) return;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
@@ -105,17 +114,20 @@ void load_driver_entry_points() {
   g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
 }
 
-// Brings up the per-device state (with `dev` current). Called under g_mutex.
+// The per-device state, brought up on first use (with `dev` current).
 DeviceState& device_state(int dev) {
   if (dev < 0 || dev >= kMaxDevices) TB_FAIL(TRACEA_INVALID_PARAMS, "device_id %d out of range", dev);
   DeviceState& st = g_dev[dev];
-  if (st.ready) return st;
+  if (st.ready.load(std::memory_order_acquire)) return st;
+  std::lock_guard<std::mutex> lock(g_dev_mu[dev]);
+  if (st.ready.load(std::memory_order_relaxed)) return st;
   cudaDeviceProp prop;
   TB_CUDA(cudaGetDeviceProperties(&prop, dev));
   if (prop.major != 10)
     TB_FAIL(TRACEA_UNSUPPORTED_CONFIG,
             "device %d is sm_%d%d; this library only carries sm_100a kernels", dev, prop.major,
             prop.minor);
+  st.dev = dev;
   st.num_sms = prop.multiProcessorCount;
   load_driver_entry_points();
   cudaMemPoolProps pp = {};
@@ -129,7 +141,7 @@ DeviceState& device_state(int dev) {
   TB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&st.status), 4 * sizeof(uint32_t),
                         cudaHostAllocMapped | cudaHostAllocPortable));
   memset(st.status, 0, 4 * sizeof(uint32_t));
-  st.ready = true;
+  st.ready.store(true, std::memory_order_release);
   return st;
 }
 
@@ -311,9 +323,10 @@ void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, 
                 cudaStream_t stream) {
   auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN, kPair, kRows2, kCoop>;
   constexpr int kVariant = (kPair ? 1 : (kRows2 ? 2 : 0)) + (kCoop ? 3 : 0);
-  if (!st.attr_set[dt_idx][bn_idx][kVariant]) {
+  std::atomic<bool>& attr_done = g_attr_set[st.dev][dt_idx][bn_idx][kVariant];
+  if (!attr_done.load(std::memory_order_relaxed)) {
     TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
-    st.attr_set[dt_idx][bn_idx][kVariant] = true;
+    attr_done.store(true, std::memory_order_relaxed);
   }
   if constexpr (kPair) {
     // clusters of two CTAs on neighbouring SMs; no multicast is used anywhere in the kernel
@@ -413,6 +426,10 @@ const Knobs& knobs() {
 // handle; the device address kernels must be given comes from cudaGetSymbolAddress (noalloc_state).
 constexpr size_t kStaticScratchBytes = 16u << 20;   // 16 MiB
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+// Error words of the kernels tracea_conv2d_noalloc launches ({code, block, detail, 0}, first error wins). The
+// allocating path keeps its words in pinned host memory; this path may not allocate, so its words live in the
+// device image as well and tracea_b200_device_status copies them back on request.
+static __device__ __align__(16) uint32_t g_noalloc_status[4];
 
 // Bump allocator over the static array for the duration of one call.
 struct StaticArena {
@@ -432,19 +449,21 @@ struct StaticArena {
 };
 
 struct NoAllocState {
-  bool ready = false;
+  std::atomic<bool> ready{false};
   int num_sms = 0;
   unsigned char* scratch = nullptr;   // device address of g_static_scratch on this device
-  bool attr_set[3][3][6] = {};
+  uint32_t* status = nullptr;         // device address of g_noalloc_status on this device
 };
 NoAllocState g_noalloc[kMaxDevices];
 
-// First call on a device (with that device current, under g_mutex): queries the SM count, resolves
-// the driver entry points and the device address of the static scratch. Nothing here allocates.
+// First call on a device (with that device current): queries the SM count, resolves the driver entry
+// points and the device addresses of the static scratch and of the status words. Nothing here allocates.
 NoAllocState& noalloc_state(int dev) {
   if (dev < 0 || dev >= kMaxDevices) TB_FAIL(TRACEA_INVALID_PARAMS, "device_id %d out of range", dev);
   NoAllocState& na = g_noalloc[dev];
-  if (na.ready) return na;
+  if (na.ready.load(std::memory_order_acquire)) return na;
+  std::lock_guard<std::mutex> lock(g_dev_mu[dev]);
+  if (na.ready.load(std::memory_order_relaxed)) return na;
   int major = 0, sms = 0;
   TB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
   if (major != 10)
@@ -456,9 +475,15 @@ NoAllocState& noalloc_state(int dev) {
   if (e != cudaSuccess || addr == nullptr)
     TB_FAIL(TRACEA_CUDA_ERROR, "cudaGetSymbolAddress(g_static_scratch) failed on device %d: %s", dev,
             cudaGetErrorString(e));
+  void* status_addr = nullptr;
+  const cudaError_t e2 = cudaGetSymbolAddress(&status_addr, g_noalloc_status);
+  if (e2 != cudaSuccess || status_addr == nullptr)
+    TB_FAIL(TRACEA_CUDA_ERROR, "cudaGetSymbolAddress(g_noalloc_status) failed on device %d: %s", dev,
+            cudaGetErrorString(e2));
   na.num_sms = sms;
   na.scratch = static_cast<unsigned char*>(addr);
-  na.ready = true;
+  na.status = static_cast<uint32_t*>(status_addr);   // zero-initialised with the device image
+  na.ready.store(true, std::memory_order_release);
   return na;
 }
 
@@ -514,7 +539,6 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
 void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* bias,
                    const View4* residual, const View4& out, const CoreParams& p,
                    const Epilogue& epi) {
-  std::lock_guard<std::mutex> lock(g_mutex);
   DeviceGuard guard(dev);
   DeviceState& st = device_state(dev);
 
@@ -533,18 +557,18 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
 void conv2d_device_noalloc(int dev, const View4& x_in, const View4& w_in, const View4* bias,
                            const View4* residual, const View4& out, const CoreParams& p,
                            const Epilogue& epi) {
-  std::lock_guard<std::mutex> lock(g_mutex);
   DeviceGuard guard(dev);
   NoAllocState& na = noalloc_state(dev);
   DeviceState st;                       // a view for conv2d_core, not a registered device state
+  st.dev = dev;
   st.num_sms = na.num_sms;
-  st.status = g_dev[dev].ready ? g_dev[dev].status : nullptr;   // reuse the status word if one exists
-  memcpy(st.attr_set, na.attr_set, sizeof(st.attr_set));
+  // Device-resident status words: reading them back means waiting for the GPU, so this entry does not look at
+  // them on the way in (tracea_conv2d does, its words are in host memory); tracea_b200_device_status reports them.
+  st.status = na.status;
   StaticArena arena;
   arena.base = na.scratch;
   arena.capacity = kStaticScratchBytes;
   conv2d_core(st, &arena, x_in, w_in, bias, residual, out, p, epi);
-  memcpy(na.attr_set, st.attr_set, sizeof(st.attr_set));
 }
 
 void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const View4& w_in, const View4* bias,
@@ -1046,7 +1070,8 @@ void conv2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, cons
   int cur = 0;
   TB_CUDA(cudaGetDevice(&cur));
   cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
-  std::lock_guard<std::mutex> host_lock(g_host_path_mutex);
+  DeviceState& st_cur = device_state(cur);
+  std::lock_guard<std::mutex> host_lock(st_cur.host_mu);
   const bool use_bias = bias != nullptr && epi.bias, use_res = res != nullptr && epi.residual;
   auto image_major = [](const View4& v) {   // images do not interleave: one image's span fits in stride[0]
     long long span = 1;
@@ -1067,8 +1092,7 @@ void conv2d_checked(const TraceaTensorView& xv, const TraceaTensorView& wv, cons
   Staged sx, sw, sb, sr, so;
   DeviceState* stp = nullptr;
   {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    DeviceState& st = device_state(cur);
+    DeviceState& st = st_cur;
     stp = &st;
     stage_in(st, x, sx, stream, chunks == 1);
     stage_in(st, w, sw, stream, true);
@@ -1422,12 +1446,12 @@ void conv_transpose2d_checked(const TraceaTensorView& xv, const TraceaTensorView
   int cur = 0;
   TB_CUDA(cudaGetDevice(&cur));
   cudaStream_t stream = static_cast<cudaStream_t>(tp.stream);
-  std::lock_guard<std::mutex> host_lock(g_host_path_mutex);
+  DeviceState& st_cur = device_state(cur);
+  std::lock_guard<std::mutex> host_lock(st_cur.host_mu);
   const bool use_bias = bias != nullptr && epi.bias, use_res = res != nullptr && epi.residual;
   Staged sx, sw, sb, sr, so;
   {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    DeviceState& st = device_state(cur);
+    DeviceState& st = st_cur;
     stage_in(st, x, sx, stream, true);
     stage_in(st, w, sw, stream, true);
     if (use_bias) stage_in(st, *bias, sb, stream, true);
@@ -1595,17 +1619,16 @@ int tracea_init(void) {
     if (count <= 0) TB_FAIL(TRACEA_CUDA_ERROR, "no CUDA device");
     int cur = 0;
     TB_CUDA(cudaGetDevice(&cur));
-    std::lock_guard<std::mutex> lock(g_mutex);
     device_state(cur);
   });
   return s == TRACEA_SUCCESS ? 0 : -1;
 }
 
 void tracea_shutdown(void) {
-  std::lock_guard<std::mutex> lock(g_mutex);
   for (int d = 0; d < kMaxDevices; ++d) {
+    std::lock_guard<std::mutex> lock(g_dev_mu[d]);
     DeviceState& st = g_dev[d];
-    if (!st.ready) continue;
+    if (!st.ready.load(std::memory_order_acquire)) continue;
     int prev = 0;
     cudaGetDevice(&prev);
     cudaSetDevice(d);
@@ -1622,7 +1645,11 @@ void tracea_shutdown(void) {
     }
     if (st.pool != nullptr) cudaMemPoolDestroy(st.pool);
     if (st.status != nullptr) cudaFreeHost(st.status);
-    st = DeviceState();
+    st.pool = nullptr;
+    st.status = nullptr;
+    st.copy_in = st.copy_out = nullptr;
+    st.ev_entry = st.ev_done = nullptr;
+    st.ready.store(false, std::memory_order_release);
     cudaSetDevice(prev);
   }
 }
@@ -1645,10 +1672,46 @@ uint64_t tracea_b200_launch_count(void) { return g_kernel_launches.load(std::mem
 uint32_t tracea_b200_device_status(int32_t device_id) {
   if (device_id < 0 || device_id >= kMaxDevices) return 0;
   DeviceState& st = g_dev[device_id];
-  if (!st.ready || st.status == nullptr) return 0;
-  const uint32_t code = st.status[0];
-  if (code != 0u) memset(st.status, 0, 4 * sizeof(uint32_t));
+  uint32_t code = 0;
+  if (st.ready.load(std::memory_order_acquire) && st.status != nullptr) {
+    code = st.status[0];
+    if (code != 0u) memset(st.status, 0, 4 * sizeof(uint32_t));
+  }
+  // the no-alloc entry's words are in device memory: a blocking copy, which is why this is a call to make after
+  // synchronising and not on a latency path
+  NoAllocState& na = g_noalloc[device_id];
+  if (na.ready.load(std::memory_order_acquire) && na.status != nullptr) {
+    int prev = -1;
+    if (cudaGetDevice(&prev) == cudaSuccess && (prev == device_id || cudaSetDevice(device_id) == cudaSuccess)) {
+      uint32_t words[4] = {0, 0, 0, 0};
+      if (cudaMemcpy(words, na.status, sizeof(words), cudaMemcpyDeviceToHost) == cudaSuccess && words[0] != 0u) {
+        if (code == 0u) code = words[0];
+        cudaMemset(na.status, 0, sizeof(words));
+      }
+      if (prev != device_id) cudaSetDevice(prev);
+    }
+  }
   return code;
+}
+
+int32_t tracea_b200_pool_stats(int32_t device_id, uint64_t stats[4], int32_t reset_high) {
+  if (device_id < 0 || device_id >= kMaxDevices || stats == nullptr) return -1;
+  stats[0] = stats[1] = stats[2] = stats[3] = 0;
+  DeviceState& st = g_dev[device_id];
+  if (!st.ready.load(std::memory_order_acquire) || st.pool == nullptr) return 0;   // no pool yet: all zeros
+  const cudaMemPoolAttr attrs[4] = {cudaMemPoolAttrReservedMemCurrent, cudaMemPoolAttrReservedMemHigh,
+                                    cudaMemPoolAttrUsedMemCurrent, cudaMemPoolAttrUsedMemHigh};
+  for (int i = 0; i < 4; ++i) {
+    cuuint64_t v = 0;
+    if (cudaMemPoolGetAttribute(st.pool, attrs[i], &v) != cudaSuccess) return -1;
+    stats[i] = v;
+  }
+  if (reset_high != 0) {
+    cuuint64_t zero = 0;
+    cudaMemPoolSetAttribute(st.pool, cudaMemPoolAttrReservedMemHigh, &zero);
+    cudaMemPoolSetAttribute(st.pool, cudaMemPoolAttrUsedMemHigh, &zero);
+  }
+  return 1;
 }
 
 }  // extern "C"

@@ -24,7 +24,7 @@ DTYPE_FLOAT32, DTYPE_FLOAT16, DTYPE_BFLOAT16, DTYPE_INT32, DTYPE_INT8 = 0, 1, 2,
 EXPORTED_SYMBOLS = (
     "tracea_conv2d", "tracea_conv2d_v0", "tracea_conv2d_noalloc", "tracea_get_last_error", "tracea_clear_error",
     "tracea_version_major", "tracea_version_minor", "tracea_version_patch", "tracea_init",
-    "tracea_shutdown", "tracea_b200_device_status", "tracea_b200_launch_count",
+    "tracea_shutdown", "tracea_b200_device_status", "tracea_b200_launch_count", "tracea_b200_pool_stats",
     "tracea_b200_conv_transpose_plan",
     "tracea_gemm", "tracea_conv_transpose2d", "tracea_conv2d_prepack_bytes", "tracea_conv2d_prepack",
     "tracea_gemm_prepack_b_bytes", "tracea_gemm_prepack_b",
@@ -122,6 +122,8 @@ def load():
     lib.tracea_shutdown.restype = None
     lib.tracea_b200_device_status.argtypes = [ctypes.c_int32]
     lib.tracea_b200_device_status.restype = ctypes.c_uint32
+    lib.tracea_b200_pool_stats.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_uint64), ctypes.c_int32]
+    lib.tracea_b200_pool_stats.restype = ctypes.c_int32
     lib.tracea_b200_launch_count.argtypes = []
     lib.tracea_b200_launch_count.restype = ctypes.c_uint64
     lib.tracea_b200_conv_transpose_plan.argtypes = [ctypes.c_uint32] * 5 + [ctypes.POINTER(ctypes.c_int64)]
@@ -209,6 +211,18 @@ def conv_transpose2d_raw(x, w, bias, residual, out, stride=(1, 1), padding=(0, 0
     if check and st != SUCCESS:
         raise TraceaError(st, last_error(), "tracea_conv_transpose2d")
     return st
+
+
+def pool_stats(device_id=0, reset_high=False):
+    """Scratch-pool byte counters of one device: dict(reserved, reserved_high, used, used_high), or None when
+    the device has no pool yet."""
+    buf = (ctypes.c_uint64 * 4)()
+    rc = load().tracea_b200_pool_stats(device_id, buf, 1 if reset_high else 0)
+    if rc < 0:
+        raise ValueError("bad arguments")
+    if rc == 0:
+        return None
+    return dict(zip(("reserved", "reserved_high", "used", "used_high"), (int(v) for v in buf)))
 
 
 def conv_transpose_plan(in_extent, out_extent, filt, stride, padding):
