@@ -20,7 +20,14 @@
 #define TB200_PROF_ADD(acc, t0) acc += clock64() - (t0)
 #define TB200_PROF_STORE(idx, val) \
   if (args.prof != nullptr) args.prof[blockIdx.x * 16 + (idx)] = (val)
+#define TB200_PROF_NOW(idx)                                                              \
+  if (args.prof != nullptr && threadIdx.x == 0) {                                        \
+    unsigned long long t_;                                                               \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                               \
+    args.prof[blockIdx.x * 16 + (idx)] = static_cast<long long>(t_);                     \
+  }
 #else
+#define TB200_PROF_NOW(idx)
 #define TB200_PROF_T(var)
 #define TB200_PROF_ADD(acc, t0)
 #define TB200_PROF_STORE(idx, val)
@@ -42,6 +49,7 @@ enum : uint32_t {
   kErrMmaWaitTmem = 3,    // MMA issuer: accumulator never drained
   kErrEpilogueWait = 4,   // epilogue: accumulator never became ready
   kErrResidualWait = 5,   // epilogue: a residual box never landed
+  kErrSplitWait = 6,      // epilogue: the partial sums of a tile split over K never all arrived
 };
 
 enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3 };
@@ -66,13 +74,20 @@ struct ConvKernelArgs {
   // +b_jump_s at every tap boundary, +b_jump_r more at every filter-row boundary. Dense [R][S][C] rows: all 0.
   // Non-zero jumps are only used with 128-byte chunks (one chunk per stage).
   int b_k0, b_jump_s, b_jump_r;
-  int prefetch_dist;      // > 0: the producer L2-prefetches A this many k-steps ahead of its loads
   // tiling / pipeline
   int num_m_tiles, num_n_tiles;
   int panel_width;  // column tiles per panel of the tile order (>= 1; num_n_tiles = one panel = row-major order)
   int panel_tiles;  // num_m_tiles * panel_width
   int num_stages;
   int shared_bias;  // 1: one bias copy per CTA (num_n_tiles == 1) instead of one per epilogue warp
+  // Work schedule. Tiles [0, dp_tiles) are dealt whole to the workers (CTAs, or CTA pairs) round robin. The k-steps
+  // of the remaining sk_tiles tiles -- the partly filled last wave of a large layer, or every tile of a layer with
+  // fewer tiles than SMs -- are laid end to end and cut into equal shares for the first sk_workers workers, so a
+  // tile may be computed by several workers, each over a slice of K. sk_tiles == 0: no tile is split.
+  int dp_tiles, sk_tiles, sk_workers;
+  float* sk_partials;       // fp32 partial accumulators: 2 slots per worker, sk_slot_floats each
+  uint32_t* sk_counters;    // per split tile and epilogue warp: {tickets taken, partials written}; zero at launch
+  long long sk_slot_floats;
   // tcgen05 descriptors (host-built constants)
   uint32_t idesc;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo, swizzle_mode;
@@ -95,9 +110,6 @@ struct ConvKernelArgs {
   // error reporting: 4 words {code, block, detail, 0}; first error wins
   uint32_t* status;
   long long* prof;        // cycle counters, only written by -DTB200_PROFILE builds
-#ifdef TB200_ABLATE
-  int dbg;                // bring-up builds only: bit 0 no B loads, 1 no A loads, 2 every tile reads tile 0's A, 3 no MMAs, 4 no stores
-#endif
 };
 
 template <typename T> struct OutTraits;
@@ -359,7 +371,245 @@ __device__ __noinline__ void coop_load_box(uint32_t stg, const OutT* row_base, l
   __syncwarp();   // rows were written by other lanes than the ones that read them next
 }
 
-template <typename OutT, int BN, bool kPair, bool kRows2, bool kCoop>
+// One unit of work of a worker: k-steps [k_begin, k_end) of tile `tile`. A whole tile has k_begin == 0 and
+// k_end == k_iters; anything else is one piece of a tile that is split over K between several workers.
+struct WorkItem {
+  int tile, k_begin, k_end;
+};
+
+// Split region: `total` k-steps (sk_tiles * k_iters, kept below 2^30 by the host) shared by `workers` workers;
+// worker w owns [w * total / workers, (w + 1) * total / workers).
+__device__ __forceinline__ int sk_share_begin(int total, int workers, int w) {
+  return static_cast<int>(static_cast<long long>(w) * total / workers);
+}
+// The worker whose share contains position `pos` (the largest w with sk_share_begin(w) <= pos).
+__device__ __forceinline__ int sk_owner_of(int total, int workers, int pos) {
+  return static_cast<int>(((static_cast<long long>(pos) + 1) * workers - 1) / total);
+}
+
+// Walks a worker's items in the order every role of the CTA follows: first the pieces its share of the split
+// region cuts off (the tail of the tile the share starts in, the head of the tile it ends in: at most two, both
+// short), then the whole tiles of the share, then its whole tiles of the rest. The pieces come first so that the
+// exchange of partial sums and their short main loops sit in front of long main loops that hide them -- a short
+// item between two long ones would leave the tensor pipe waiting for an accumulator to drain.
+struct WorkIter {
+  int sk_b, sk_e;           // this worker's share of the split region [sk_b, sk_e), in k-steps
+  int idx;                  // items handed out so far
+  int whole_next;           // next whole tile of the share (index inside the split region)
+  int dp_next;              // next whole tile outside the split region
+  template <bool kSplit>
+  __device__ __forceinline__ void init(const ConvKernelArgs& a, int worker, int k_iters) {
+    sk_b = sk_e = 0;
+    if (kSplit && a.sk_tiles > 0 && worker < a.sk_workers) {
+      const int total = a.sk_tiles * k_iters;
+      sk_b = sk_share_begin(total, a.sk_workers, worker);
+      sk_e = sk_share_begin(total, a.sk_workers, worker + 1);
+    }
+    idx = 0;
+    whole_next = (sk_b + k_iters - 1) / k_iters;
+    dp_next = worker;
+  }
+  template <bool kSplit>
+  __device__ __forceinline__ bool next(WorkItem& it, const ConvKernelArgs& a, int num_workers, int k_iters) {
+    if constexpr (kSplit) {
+      if (sk_b < sk_e) {
+        const int tb = sk_b / k_iters, te = sk_e / k_iters;          // tiles the share starts / ends in
+        const int kb = sk_b - tb * k_iters, ke = sk_e - te * k_iters;
+        const bool has_tail = kb != 0;                               // [sk_b, end of tile tb) -- or [sk_b, sk_e)
+        const bool has_head = ke != 0 && !(has_tail && te == tb);    // [start of tile te, sk_e)
+        const int n_pieces = (has_tail ? 1 : 0) + (has_head ? 1 : 0);
+        if (idx < n_pieces) {
+          if (idx == 0 && has_tail) {
+            it.tile = a.dp_tiles + tb;
+            it.k_begin = kb;
+            it.k_end = te == tb ? ke : k_iters;
+          } else {
+            it.tile = a.dp_tiles + te;
+            it.k_begin = 0;
+            it.k_end = ke;
+          }
+          ++idx;
+          return true;
+        }
+        if (whole_next < te) {
+          it.tile = a.dp_tiles + whole_next++;
+          it.k_begin = 0;
+          it.k_end = k_iters;
+          ++idx;
+          return true;
+        }
+      }
+    }
+    if (dp_next < a.dp_tiles) {
+      it.tile = dp_next;
+      it.k_begin = 0;
+      it.k_end = k_iters;
+      dp_next += num_workers;
+      ++idx;
+      return true;
+    }
+    return false;
+  }
+};
+
+// Slot `end` (1: the piece starts at the tile's first k-step) of worker w in the partial-sum scratch. Inside a
+// slot: [epilogue-warp position 0..7][32-column chunk][8][lane] float4, so that every load / store instruction of
+// a warp covers 512 contiguous bytes.
+__device__ __forceinline__ float4* sk_slot(const ConvKernelArgs& a, int w, int end) {
+  return reinterpret_cast<float4*>(a.sk_partials + (2LL * w + end) * a.sk_slot_floats);
+}
+
+// ---- exchange of partial sums between the pieces of a tile that is split over K (one epilogue warp's part: the
+// warp owns 32 rows x `chunks` * 32 columns of the accumulator at TMEM address taddr0). Every piece takes a ticket
+// per warp position. All but the last ticket write their fp32 accumulators to their slot of the scratch
+// (sk_dump_partial), hand the TMEM buffer back and count themselves done. The last ticket keeps its accumulator,
+// waits until the others are done -- they all hold earlier tickets, so they are running their stores right now
+// and wait for nobody: no piece ever waits for a CTA that is not running -- then adds the partial sums in piece
+// order (its own taken at its position, so the result does not depend on which piece came last), writes the total
+// back to TMEM (sk_reduce_two / sk_reduce_many) and runs the ordinary epilogue on it. The counters are left at
+// zero for the next launch. Each step is a function of its own, out of line: the kernel has 168 registers per
+// thread and a spilled register goes all the way to L2 (shared memory leaves the L1 almost no room), so neither
+// the epilogue nor any of these may be made to spill by the others.
+
+// Writes the warp's accumulator to `dst` (this lane's first float4 of the warp's region of a slot) and hands the
+// TMEM buffer back (arrive on `release_bar`, a shared::cluster address when kPair) once the last chunk is in registers.
+template <bool kPair>
+__device__ __noinline__ void sk_dump_partial(uint32_t taddr0, int chunks, float4* dst, uint32_t release_bar, int lane) {
+  using namespace ptx;
+#pragma unroll 1
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr0 + c * 32, v);
+    tmem_ld_wait();
+    if (c == chunks - 1) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kPair) mbar_arrive_cluster(release_bar);
+        else mbar_arrive(release_bar);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      __stcg(dst + (c * 8 + q) * 32,
+             make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
+                         __uint_as_float(v[4 * q + 3])));
+  }
+}
+
+// Lane 0 waits until `expected` other pieces have counted themselves done on cnt[1], then zeroes the tile's two
+// counters (every party has passed both by then). False when the wait gave up.
+__device__ __noinline__ bool sk_wait_partials(uint32_t* cnt, uint32_t expected, volatile uint32_t* abort_flag, int lane) {
+  bool all_in = true;
+  if (lane == 0) {
+    const long long t_start = clock64();
+    uint32_t spins = 0;
+    while (ptx::ld_acquire_gpu(cnt + 1) != expected) {
+      if ((++spins & 0xffu) == 0 && (*abort_flag != 0u || clock64() - t_start > kWaitLimitCycles)) {
+        all_in = false;
+        break;
+      }
+    }
+    if (all_in) {
+      cnt[0] = 0u;
+      cnt[1] = 0u;
+    }
+  }
+  // lane 0's acquire load, then the warp-wide vote: the other lanes' reads below come after both
+  all_in = __all_sync(0xffffffffu, all_in);
+  return all_in;
+}
+
+// Two pieces (a split region of more than one wave never cuts a tile into more): own + other, which is the same
+// number whichever of the two does the adding. `src` is this lane's first float4 of the other piece's values; the
+// block of the next chunk is in flight while this chunk is added and written back.
+__device__ __noinline__ void sk_reduce_two(uint32_t taddr0, int chunks, const float4* src) {
+  using namespace ptx;
+  float4 nb[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) nb[q] = __ldcg(src + q * 32);
+#pragma unroll 1
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr0 + c * 32, v);
+    float4 cur[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) cur[q] = nb[q];
+    if (c + 1 < chunks) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) nb[q] = __ldcg(src + (c + 1) * 256 + q * 32);
+    }
+    tmem_ld_wait();
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + cur[q].x);
+      v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + cur[q].y);
+      v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + cur[q].z);
+      v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + cur[q].w);
+    }
+    tmem_st_32x32(taddr0 + c * 32, v);
+  }
+  tmem_st_wait();
+}
+
+// Any number of pieces, added in piece order: pieces 0 .. me-1 from scratch, this piece's own values from TMEM,
+// pieces me+1 .. from scratch. `first` is the worker of piece 0, `warp_off` the lane's float4 offset inside a slot.
+// (One block of 32 columns is fetched while the previous one is added; layers with fewer tiles than SMs, whose
+// tiles are cut into three or more pieces, come through here.)
+__device__ __noinline__ void sk_reduce_many(const ConvKernelArgs& a, uint32_t taddr0, int chunks, int first, int pieces,
+                                            int me, long long warp_off) {
+  using namespace ptx;
+#pragma unroll 1
+  for (int c = 0; c < chunks; ++c) {
+    float acc[32];
+    float4 nb[8];
+    // a tile's first piece starts at k-step 0 (slot end 1); every later piece is the head of its worker's share
+    auto fetch = [&](int pc) {
+      const float4* src = sk_slot(a, first + pc, pc == 0 ? 1 : 0) + warp_off + c * 256;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) nb[q] = __ldcg(src + q * 32);
+    };
+    auto own_values = [&](bool init) {
+      uint32_t v[32];
+      tmem_ld_32x32(taddr0 + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] = init ? __uint_as_float(v[j]) : acc[j] + __uint_as_float(v[j]);
+    };
+    if (me != 0) fetch(0);
+#pragma unroll 1
+    for (int pc = 0; pc < pieces; ++pc) {
+      if (pc == me) {
+        own_values(pc == 0);
+        if (pc == 0 && pieces > 1) fetch(1);
+        continue;
+      }
+      float4 cur[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) cur[q] = nb[q];
+      const int nxt = pc + 1 == me ? pc + 2 : pc + 1;   // next piece that comes from scratch
+      if (nxt < pieces) fetch(nxt);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (pc == 0) {
+          acc[4 * q] = cur[q].x; acc[4 * q + 1] = cur[q].y; acc[4 * q + 2] = cur[q].z; acc[4 * q + 3] = cur[q].w;
+        } else {
+          acc[4 * q] += cur[q].x; acc[4 * q + 1] += cur[q].y; acc[4 * q + 2] += cur[q].z; acc[4 * q + 3] += cur[q].w;
+        }
+      }
+    }
+    uint32_t v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[j]);
+    tmem_st_32x32(taddr0 + c * 32, v);
+  }
+  tmem_st_wait();
+}
+
+// kSplit: the launch cuts some tiles over K (ConvKernelArgs::sk_tiles > 0). A separate instantiation, so that the
+// launches that split nothing -- most of them -- carry none of the exchange code: the call to it alone costs the
+// epilogue registers, and a spilled register here goes all the way to L2.
+template <typename OutT, int BN, bool kPair, bool kRows2, bool kCoop, bool kSplit>
 __global__ void __launch_bounds__(kNumThreads, 1)
 conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ CUtensorMap tmap_w,
@@ -384,6 +634,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   constexpr uint32_t kTmemCols = 2 * kAccCols;           // double-buffered: 128, 256 or 512 columns
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
 
+  TB200_PROF_NOW(12);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -439,11 +690,16 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_p;
+  // Everything above touched only this CTA's shared memory, TMEM and the kernel's own parameters, so under a
+  // programmatic dependent launch it overlaps the tail of the previous kernel on the stream. From here on global
+  // memory is read and written: wait for that kernel to finish (a no-op without such a dependency). The next
+  // kernel may be scheduled onto SMs as this grid's CTAs leave them; it waits at the same point.
+  griddep_launch_dependents();
+  griddep_wait();
+  TB200_PROF_NOW(13);
 
-  const int num_tiles = args.num_m_tiles * args.num_n_tiles;
   const int chunks_per_stage = kStageKBytes / args.chunk_bytes;
   const int k_iters = (args.total_chunks + chunks_per_stage - 1) / chunks_per_stage;
-
   // Tile order: the output is cut into panels of `panel_width` column tiles; inside a panel tiles run row by row.
   // One wave of CTAs then works on a block of rows x panel_width columns whose A rows and B columns stay in L2
   // (with a single panel -- panel_width = num_n_tiles -- this is plain row-major order). Two divisions per tile.
@@ -477,43 +733,11 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       (void)prof_wait;
       TB200_PROF_T(prof_t0);
       bool slot_free = mbar_test_wait(empty_addr, phase ^ 1u);
-      // L2 prefetch cursor: walks the same (tile, k-step) sequence as the loads, `prefetch_dist` steps ahead
-      struct {
-        int tile, m_tile, n_tile, it, w_start, h_start, img0, c_coord, tap_s;
-        uint32_t off_w, off_h;
-      } pf = {};
-      auto pf_begin_tile = [&]() {
-        tile_coords(pf.tile, pf.m_tile, pf.n_tile);
-        const int pm0 = args.m_begin + pf.m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
-        const int pt = pm0 / args.Wo;
-        pf.w_start = (pm0 % args.Wo) * args.stride_w - args.pad_w;
-        pf.h_start = (pt % args.Ho) * args.stride_h - args.pad_h;
-        pf.img0 = pt / args.Ho;
-        pf.it = 0; pf.c_coord = 0; pf.tap_s = 0; pf.off_w = 0; pf.off_h = 0;
-      };
-      auto pf_step = [&]() {   // issue one prefetch (if any work is left) and advance
-        if (pf.tile >= num_tiles) return;
-        tma_prefetch_im2col_4d(&tmap_x, pf.c_coord, pf.w_start, pf.h_start, pf.img0, (uint16_t)pf.off_w,
-                               (uint16_t)pf.off_h);
-        pf.c_coord += args.chunk_elems;
-        if (pf.c_coord == args.C) {
-          pf.c_coord = 0;
-          pf.off_w += args.dil_w;
-          if (++pf.tap_s == args.S) { pf.tap_s = 0; pf.off_w = 0; pf.off_h += args.dil_h; }
-        }
-        if (++pf.it == k_iters) {
-          pf.tile += num_workers;
-          if (pf.tile < num_tiles) pf_begin_tile();
-        }
-      };
-      const bool do_prefetch = one_chunk && args.prefetch_dist > 0;
-      if (do_prefetch) {
-        pf.tile = worker;
-        if (pf.tile < num_tiles) pf_begin_tile();
-        for (int i = 0; i < args.prefetch_dist; ++i) pf_step();
-      }
-      for (int tile = worker; tile < num_tiles && ok; tile += num_workers) {
-        tile_coords(tile, m_tile, n_tile);
+      WorkIter witer;
+      witer.template init<kSplit>(args, worker, k_iters);
+      WorkItem item;
+      while (ok && witer.template next<kSplit>(item, args, num_workers, k_iters)) {
+        tile_coords(item.tile, m_tile, n_tile);
         const int m0 = args.m_begin + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;   // this CTA's 128 pixels
         const int q0 = m0 % args.Wo;
         const int t = m0 / args.Wo;
@@ -531,10 +755,21 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           img1 = t1 / args.Ho;
         }
         if (one_chunk) {
-          // common case: one 128-byte chunk per stage = 64 (16-bit) or 32 (fp32) channels of one tap
+          // common case: one 128-byte chunk per stage = 64 (16-bit) or 32 (fp32) channels of one tap.
+          // Position of k-step k_begin: tap (r, s), channel chunk cc (a whole tile starts at 0, 0, 0)
           int c_coord = 0, k_coord = args.b_k0, tap_s = 0;
           uint32_t off_w = 0, off_h = 0;
-          for (int it = 0; it < k_iters; ++it) {
+          if (item.k_begin != 0) {
+            const int tap = item.k_begin / args.chunks_per_tap;
+            const int cc = item.k_begin - tap * args.chunks_per_tap;
+            const int tap_r = tap / args.S;
+            tap_s = tap - tap_r * args.S;
+            c_coord = cc * args.chunk_elems;
+            off_w = static_cast<uint32_t>(tap_s * args.dil_w);
+            off_h = static_cast<uint32_t>(tap_r * args.dil_h);
+            k_coord += item.k_begin * args.chunk_elems + tap * args.b_jump_s + tap_r * args.b_jump_r;
+          }
+          for (int it = item.k_begin; it < item.k_end; ++it) {
             TB200_PROF_T(tw);
             if (!slot_free && !mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) {
               report_error(args, abort_p, kErrProducerWait, (uint32_t)it);
@@ -546,35 +781,6 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             uint32_t nstage = stage_addr + kStageBytes, nfull = full_addr + 8u, nempty = empty_addr + 8u, nphase = phase;
             if (nstage == ring_end) { nstage = smem_base; nfull = full_bar0; nempty = empty_bar0; nphase ^= 1u; }
             bool next_free;
-#ifdef TB200_ABLATE
-            if constexpr (kPair) {
-              if (args.dbg & 7) {
-                const bool no_b = args.dbg & 1, no_a = args.dbg & 2;
-                const int img_a = (args.dbg & 4) ? 0 : img0;
-                const int w_a = (args.dbg & 4) ? (int)cta_rank * kBlockM * 0 - args.pad_w : w_start;
-                const int h_a = (args.dbg & 4) ? -args.pad_h : h_start;
-                const uint32_t bytes = (no_a ? 0u : kABytes) + (no_b ? 0u : kBBytes);
-                next_free = mbar_test_wait(nempty, nphase ^ 1u);
-                const uint32_t fl = full_leader0 + (full_addr - full_bar0);
-                if (leader) mbar_arrive_expect_tx(full_addr, 2u * bytes);
-                if (!no_a)
-                  asm volatile(
-                      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
-                      " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(stage_addr),
-                      "l"(reinterpret_cast<uint64_t>(&tmap_x)), "r"(fl), "r"(c_coord), "r"(w_a), "r"(h_a), "r"(img_a),
-                      "h"((uint16_t)off_w), "h"((uint16_t)off_h)
-                      : "memory");
-                if (!no_b)
-                  asm volatile(
-                      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-                      " [%0], [%1, {%3, %4}], [%2];" ::"r"(stage_addr + kABytes),
-                      "l"(reinterpret_cast<uint64_t>(&tmap_w)), "r"(fl), "r"(k_coord), "r"(n_coord)
-                      : "memory");
-                if (bytes == 0u && leader) { /* nothing in flight: the expect_tx(0) arrive completes the phase */ }
-                goto stage_issued;
-              }
-            }
-#endif
             if constexpr (kPair) {
               // both CTAs' copies complete on the leader's full barrier; the leader arms it for both
               next_free = tma_stage_probe_pair(stage_addr, stage_addr + kABytes, full_addr,
@@ -591,10 +797,6 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                           w_start, h_start, img0, (uint16_t)off_w, (uint16_t)off_h, &tmap_w, k_coord,
                                           n_coord, nempty, nphase ^ 1u);
             }
-#ifdef TB200_ABLATE
-          stage_issued:
-#endif
-            if (do_prefetch) pf_step();
             k_coord += args.chunk_elems;
             c_coord += args.chunk_elems;
             if (c_coord == args.C) {
@@ -608,6 +810,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             slot_free = next_free;
           }
         } else {
+          // narrow k-chunks (several per stage): whole tiles only, the host never splits these over K
           int chunk = 0, tap_r = 0, tap_s = 0, cc = 0;
           for (int it = 0; it < k_iters; ++it) {
             if (!mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) {
@@ -689,7 +892,10 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       (void)prof_wfull; (void)prof_wtmem;
       TB200_PROF_T(prof_t0);
       bool stage_ready = mbar_test_wait(full_addr, phase);
-      for (int tile = worker; tile < num_tiles && ok; tile += num_workers, ++local_tile) {
+      WorkIter witer;
+      witer.template init<kSplit>(args, worker, k_iters);
+      WorkItem item;
+      for (; ok && witer.template next<kSplit>(item, args, num_workers, k_iters); ++local_tile) {
         const int buf = local_tile & 1;
         const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
         TB200_PROF_T(tw0);
@@ -701,7 +907,8 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         TB200_PROF_ADD(prof_wtmem, tw0);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf) * kAccCols;
-        for (int it = 0; it < k_iters; ++it) {
+        for (int it = item.k_begin; it < item.k_end; ++it) {
+          const bool first = it == item.k_begin;   // the piece's first MMA overwrites the accumulator
           TB200_PROF_T(tw1);
           if (!stage_ready && !mbar_wait_bounded(full_addr, phase, abort_p, kWaitLimitCycles)) {
             report_error(args, abort_p, kErrMmaWaitFull, (uint32_t)it);
@@ -715,7 +922,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           tc_fence_after();
           bool next_ready;
           if constexpr (kRows2) {
-            if (it == 0)
+            if (first)
               next_ready = mma_stage8_probe<kTf32, false>(d_tmem, d_tmem + BN, a_k[0] + s_off, a_k[1] + s_off,
                                                           a_k[2] + s_off, a_k[3] + s_off, kABlockBytes >> 4,
                                                           b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off, b_k[3] + s_off,
@@ -726,7 +933,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                          b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off, b_k[3] + s_off,
                                                          desc_hi, idesc, empty_addr, nfull, nphase);
           } else if constexpr (kPair) {
-            if (it == 0)
+            if (first)
               next_ready = mma_stage4_probe_pair<kTf32, false>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
                                                                a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off,
                                                                b_k[2] + s_off, b_k[3] + s_off, desc_hi, idesc,
@@ -737,7 +944,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                               b_k[2] + s_off, b_k[3] + s_off, desc_hi, idesc,
                                                               empty_addr, nfull, nphase);
           } else {
-            if (it == 0)
+            if (first)
               next_ready = mma_stage4_probe<kTf32, false>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
                                                           a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off,
                                                           b_k[3] + s_off, desc_hi, idesc, empty_addr, nfull, nphase);
@@ -802,16 +1009,42 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         bias_next[j] = b;
       }
     };
-    // this group's tiles: worker + (egroup + 2 i) * num_workers -- or, with two-row-block tiles, every tile of
-    // the worker, of which the group takes the 128-row block `egroup`
-    const int etile0 = kRows2 ? worker : worker + egroup * num_workers;
-    const int estride = kRows2 ? num_workers : 2 * num_workers;
+    // This group's items: every second item of the worker (group e drains TMEM accumulator e) -- or, with
+    // two-row-block tiles, every item, of which the group takes the 128-row block `egroup`. The iterator runs one
+    // item ahead so that the next tile's bias can be fetched early.
+    WorkIter witer;
+    witer.template init<kSplit>(args, worker, k_iters);
+    int local_next = 0;                            // local index of the item witer.next() yields next
+    auto next_mine = [&](WorkItem& it, int& local) -> bool {
+      while (witer.template next<kSplit>(it, args, num_workers, k_iters)) {
+        const int l = local_next++;
+        if (kRows2 || (l & 1) == egroup) {
+          local = l;
+          return true;
+        }
+      }
+      return false;
+    };
+    WorkItem item = {0, 0, 0};
     int m_tile = 0, n_tile = 0;
-    if (etile0 < num_tiles) {
-      tile_coords(etile0, m_tile, n_tile);
-      fetch_bias(n_tile);
-    }
-    int local_tile = kRows2 ? 0 : egroup;
+    // bias of the next item of this group, if its column tile differs from `cur_n` (-1: always): looked up on a
+    // copy of the iterator, so that no look-ahead state stays live across the epilogue body
+    auto prefetch_next_bias = [&](int cur_n) {
+      WorkIter pk = witer;
+      int pl = local_next;
+      WorkItem ni;
+      while (pk.template next<kSplit>(ni, args, num_workers, k_iters)) {
+        const int l = pl++;
+        if (kRows2 || (l & 1) == egroup) {
+          int mm, nn;
+          tile_coords(ni.tile, mm, nn);
+          if (nn != cur_n) fetch_bias(nn);
+          return;
+        }
+      }
+    };
+    prefetch_next_bias(-1);
+    int local_tile = 0;
     bool ok = true;
     long long prof_wacc = 0, prof_wres = 0, prof_ld = 0, prof_math = 0, prof_stage = 0, prof_wstore = 0;
     (void)prof_wacc; (void)prof_wres; (void)prof_ld; (void)prof_math; (void)prof_stage; (void)prof_wstore;
@@ -823,7 +1056,68 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // residual load instruction covers 4 whole 128-byte rows. A separate instantiation, because inside the TMA
     // kernels this code cost 1.3 % through register spills.
     const bool res_staged = res_tma || (kCoop && res != nullptr);
-    for (int tile = etile0; tile < num_tiles && ok; tile += estride, local_tile += (kRows2 ? 1 : 2)) {
+    // ---- exchange of partial sums, ahead of the main loop. The pieces of split tiles are the first (at most two)
+    // items of a worker. For each piece this warp owns rows of: wait for its accumulator, take a ticket, then either
+    // write the partial sums out and release the accumulator (bit stays 0: the main loop skips the item), or -- last
+    // ticket -- add the others' partial sums into the accumulator in TMEM (bit set: the main loop treats the item
+    // as a whole tile). Kept out of the main loop so that its calls cost the loop no registers.
+    uint32_t sk_reduced = 0;
+    if constexpr (kSplit) {
+      WorkIter pre;
+      pre.template init<kSplit>(args, worker, k_iters);
+      WorkItem pi;
+      for (int l = 0; ok && l < 2 && pre.template next<kSplit>(pi, args, num_workers, k_iters); ++l) {
+        if (pi.k_end - pi.k_begin == k_iters) break;          // whole tiles from here on
+        if (!kRows2 && (l & 1) != egroup) continue;           // the other group's item
+        const int buf = kRows2 ? (l & 1) : egroup;
+        const bool ready = mbar_wait_bounded(tfull_bar(buf), 0u, abort_p, kWaitLimitCycles);   // first use of the buffer
+        if (!__all_sync(0xffffffffu, ready)) {
+          if (lane == 0) report_error(args, abort_p, kErrEpilogueWait, (uint32_t)l);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                static_cast<uint32_t>(buf) * kAccCols + (kRows2 ? static_cast<uint32_t>(egroup * BN) : 0u);
+        const int sk_t = pi.tile - args.dp_tiles;
+        const int sk_total = args.sk_tiles * k_iters;
+        const int sk_first = sk_owner_of(sk_total, args.sk_workers, sk_t * k_iters);
+        const int sk_pieces = sk_owner_of(sk_total, args.sk_workers, sk_t * k_iters + k_iters - 1) - sk_first + 1;
+        const int sk_me = worker - sk_first;
+        const int row_block = kPair ? static_cast<int>(cta_rank) : (kRows2 ? egroup : 0);
+        const int sk_pos = row_block * 4 + quarter;   // which 32 rows of the tile this warp owns, 0..7
+        uint32_t* cnt = args.sk_counters + (static_cast<long long>(sk_t) * 8 + sk_pos) * 2;
+        const long long warp_off = static_cast<long long>(sk_pos) * (BN / 32) * 256 + lane;   // float4s inside a slot
+        uint32_t ticket = 0;
+        if (lane == 0) ticket = atomicAdd(cnt, 1u);
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
+        if (ticket + 1u != static_cast<uint32_t>(sk_pieces)) {
+          TB200_PROF_T(tsd);
+          sk_dump_partial<kPair>(taddr0, BN / 32, sk_slot(args, worker, pi.k_begin == 0 ? 1 : 0) + warp_off,
+                                 kPair ? mapa_cluster(tempty_bar(buf), 0u) : tempty_bar(buf), lane);
+          // every lane's stores, then the warp barrier, then lane 0's release at GPU scope (no full fence: a
+          // sequentially consistent one waits for every copy the SM has in flight)
+          __syncwarp();
+          if (lane == 0) red_release_gpu_add(cnt + 1, 1u);
+          TB200_PROF_ADD(prof_wres, tsd);
+          continue;
+        }
+        TB200_PROF_T(tsw);
+        if (!sk_wait_partials(cnt, static_cast<uint32_t>(sk_pieces - 1), abort_p, lane)) {
+          if (lane == 0) report_error(args, abort_p, kErrSplitWait, (uint32_t)l);
+          ok = false;
+          break;
+        }
+        if (sk_pieces == 2)
+          sk_reduce_two(taddr0, BN / 32, sk_slot(args, sk_first + 1 - sk_me, sk_me == 0 ? 0 : 1) + warp_off);
+        else
+          sk_reduce_many(args, taddr0, BN / 32, sk_first, sk_pieces, sk_me, warp_off);
+        TB200_PROF_ADD(prof_wstore, tsw);
+        sk_reduced |= 1u << l;
+      }
+    }
+    while (ok && next_mine(item, local_tile)) {
+      const int tile = item.tile;
       tile_coords(tile, m_tile, n_tile);
       const int buf = kRows2 ? (local_tile & 1) : egroup;
       const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
@@ -840,11 +1134,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         __syncwarp();
         bias_tile = n_tile;
       }
-      if (tile + estride < num_tiles) {
-        int mm, nn;
-        tile_coords(tile + estride, mm, nn);
-        if (nn != n_tile) fetch_bias(nn);
-      }
+      prefetch_next_bias(n_tile);
 
       const int m = args.m_begin + m_tile * kTileM + row_block * kBlockM + row;
       const bool row_ok = m < args.M;
@@ -861,13 +1151,21 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
       // Residual box of the tile's first live group: requested before the accumulator is waited for.
       // Box `box` was last stored from two groups ago; only the newer store may still be pending.
-      if (res_tma && n_base < args.K_out) {
-        if (lane == 0) {
-          bulk_wait_group_read<1>();
-          mbar_arrive_expect_tx(res_bar(ew, box), kStagingBoxBytes);
-          tma_load_2d(stg0 + box * kStagingBoxBytes, &tmap_res, res_bar(ew, box), n_base, m_row0);
+      auto request_first_residual = [&]() {
+        if (res_tma && n_base < args.K_out) {
+          if (lane == 0) {
+            bulk_wait_group_read<1>();
+            mbar_arrive_expect_tx(res_bar(ew, box), kStagingBoxBytes);
+            tma_load_2d(stg0 + box * kStagingBoxBytes, &tmap_res, res_bar(ew, box), n_base, m_row0);
+          }
         }
+      };
+      const bool partial = kSplit && item.k_end - item.k_begin != k_iters;   // one piece of a tile split over K
+      if constexpr (kSplit) {
+        // a piece whose partial sums went to another CTA is finished; one that collected the others' is a whole tile now
+        if (partial && ((sk_reduced >> local_tile) & 1u) == 0u) continue;
       }
+      if (!partial) request_first_residual();
 
       TB200_PROF_T(tw2);
       const bool ready = mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_p, kWaitLimitCycles);
@@ -881,6 +1179,10 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t taddr0 =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf) * kAccCols +
           (kRows2 ? static_cast<uint32_t>(egroup * BN) : 0u);
+
+      if constexpr (kSplit) {
+        if (partial) request_first_residual();   // the exchange left the tile's total in TMEM: an ordinary tile now
+      }
 
 #pragma unroll 1
       for (int g = 0; g < kGroups; ++g) {
@@ -1018,11 +1320,13 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   tc_fence_before();
   if constexpr (kPair) cluster_sync();   // neither CTA frees TMEM or exits while the other may still use the pair
   else __syncthreads();
+  TB200_PROF_NOW(14);
   if (warp == 1) {
     tc_fence_after();
     if constexpr (kPair) tmem_dealloc_pair<kTmemCols>(tmem_base);
     else tmem_dealloc<kTmemCols>(tmem_base);
   }
+  TB200_PROF_NOW(15);
 }
 
 }  // namespace tb200

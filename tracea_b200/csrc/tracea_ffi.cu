@@ -18,6 +18,8 @@
 #include <exception>
 #include <mutex>
 #include <string>
+#include <thread>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/tracea_b200.h"
@@ -76,6 +78,12 @@ struct DeviceState {
   cudaMemPool_t pool = nullptr;
   uint32_t* status = nullptr;  // pinned, mapped: kernels write error codes the host reads directly
   std::mutex host_mu;          // one host-memory call at a time per device (it owns the copy streams below)
+  // Scratch of the K-split schedule (fp32 partial sums, then the counters), one block per stream that has used it:
+  // launches on one stream run one after another, so they can share a block, and the kernels leave the counters
+  // at zero, so nothing has to be cleared between launches. Allocated once per stream with cudaMalloc.
+  std::mutex ws_mu;
+  std::unordered_map<unsigned long long, void*> split_ws;
+  size_t split_partial_bytes = 0, split_counter_bytes = 0;
   // host-memory path only: copy streams and events for the chunked H2D / compute / D2H pipeline
   static constexpr int kMaxChunks = 16;
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -91,9 +99,9 @@ std::mutex g_dev_mu[kMaxDevices];
 std::mutex g_driver_mu;
 DeviceState g_dev[kMaxDevices];
 // "opt-in shared memory size has been set for this kernel variant on this device":
-// [device][dtype][bn index][tiling: single CTA / CTA pair / two row blocks, x2 for the coop epilogue].
+// [device][dtype][bn index][tiling: single CTA / CTA pair / two row blocks; x3: plain, coop epilogue, K-split].
 // Setting the attribute twice is harmless, so a relaxed flag is enough.
-std::atomic<bool> g_attr_set[kMaxDevices][3][3][6];
+std::atomic<bool> g_attr_set[kMaxDevices][3][3][9];
 std::atomic<unsigned long long> g_kernel_launches{0};   // every kernel this library has launched (conv + layout adapters)
 EncodeTiledFn g_encode_tiled = nullptr;
 EncodeIm2colFn g_encode_im2col = nullptr;
@@ -129,6 +137,9 @@ DeviceState& device_state(int dev) {
             prop.minor);
   st.dev = dev;
   st.num_sms = prop.multiProcessorCount;
+  // the largest split any launch can ask for: 2 slots per worker of 256 x 256 fp32, 8 counter pairs per split tile
+  st.split_partial_bytes = 2ull * st.num_sms * 256 * 256 * sizeof(float);
+  st.split_counter_bytes = 2 * static_cast<size_t>(st.num_sms) * 8 * 2 * sizeof(uint32_t);   // up to two waves of tiles
   load_driver_entry_points();
   cudaMemPoolProps pp = {};
   pp.allocType = cudaMemAllocationTypePinned;
@@ -175,6 +186,30 @@ struct Scratch {
     if (ptr != nullptr) cudaFreeAsync(ptr, stream);
   }
 };
+
+// The K-split scratch block of `stream` on this device (created on first use). A block's counters start at zero
+// and every kernel leaves them at zero. Not for launches that are being captured into a graph: those take
+// stream-ordered pool memory, which the graph owns.
+void* split_workspace(DeviceState& st, cudaStream_t stream) {
+  unsigned long long key = reinterpret_cast<unsigned long long>(stream);
+  if (stream == cudaStreamPerThread)   // one handle, a different stream in every host thread
+    key ^= static_cast<unsigned long long>(std::hash<std::thread::id>()(std::this_thread::get_id())) << 8;
+  std::lock_guard<std::mutex> lock(st.ws_mu);
+  auto it = st.split_ws.find(key);
+  if (it != st.split_ws.end()) return it->second;
+  void* base = nullptr;
+  TB_CUDA(cudaMalloc(&base, st.split_partial_bytes + st.split_counter_bytes));
+  TB_CUDA(cudaMemset(static_cast<char*>(base) + st.split_partial_bytes, 0, st.split_counter_bytes));
+  st.split_ws.emplace(key, base);
+  return base;
+}
+
+// After a kernel gave up a wait its counters may be anywhere: clear every block of the device.
+void reset_split_workspaces(DeviceState& st) {
+  std::lock_guard<std::mutex> lock(st.ws_mu);
+  for (auto& kv : st.split_ws)
+    cudaMemset(static_cast<char*>(kv.second) + st.split_partial_bytes, 0, st.split_counter_bytes);
+}
 
 // ------------------------------------------------------------------ views
 struct View4 {
@@ -287,6 +322,30 @@ Epilogue decode_epilogue(TraceaEpilogueKind kind, bool have_bias, bool have_res)
   return e;
 }
 
+// ------------------------------------------------------------------ environment knobs
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v != nullptr && *v != '\0') ? atoi(v) : dflt;
+}
+
+// Bring-up / test knobs, read from the environment once per process (a getenv per knob per call is a measurable
+// part of the ~6 us a call costs on the host). TRACEA_B200_HOST_CHUNKS is read per call and is not in here.
+struct Knobs {
+  int force_bn, force_stages, force_chunk, no_tma_store, no_tma_residual, tiled_a, force_staging, no_window,
+      pair, rows2, panel, pdl, split_k;
+};
+const Knobs& knobs() {
+  static const Knobs k = {
+      env_int("TRACEA_B200_FORCE_BN", 0),      env_int("TRACEA_B200_FORCE_STAGES", 0),
+      env_int("TRACEA_B200_FORCE_CHUNK", 0),   env_int("TRACEA_B200_NO_TMA_STORE", 0),
+      env_int("TRACEA_B200_NO_TMA_RESIDUAL", 0), env_int("TRACEA_B200_TILED_A", 0),
+      env_int("TRACEA_B200_FORCE_STAGING", 0), env_int("TRACEA_B200_NO_WINDOW", 0),
+      env_int("TRACEA_B200_PAIR", -1),         env_int("TRACEA_B200_ROWS2", -1),
+      env_int("TRACEA_B200_PANEL", 0),         env_int("TRACEA_B200_PDL", 1),
+      env_int("TRACEA_B200_SPLIT_K", 0)};
+  return k;
+}
+
 // ------------------------------------------------------------------ tile selection
 // Relative cost of one 128-byte k-step of a 128-row x BN tile on one SM, measured on the ResNet-50 layers rather
 // than derived: the tensor pipe alone would give 512 / 256 / 192 cycles (BN/2 per MMA, 48 at BN = 64 where the
@@ -317,37 +376,58 @@ int pick_stages(int bn, bool pair, bool rows2, bool shared_bias) {
   return std::min(s, tb200::kMaxStages);
 }
 
-template <typename OutT, int BN, bool kPair, bool kRows2, bool kCoop>
-void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, const CUtensorMap& tw,
+template <typename OutT, int BN, bool kPair, bool kRows2, bool kCoop, bool kSplit>
+void launch_one_variant(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, const CUtensorMap& tw,
                 const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid, int smem,
                 cudaStream_t stream) {
-  auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN, kPair, kRows2, kCoop>;
-  constexpr int kVariant = (kPair ? 1 : (kRows2 ? 2 : 0)) + (kCoop ? 3 : 0);
+  auto kern = tb200::conv2d_igemm_sm100_kernel<OutT, BN, kPair, kRows2, kCoop, kSplit>;
+  constexpr int kVariant = (kPair ? 1 : (kRows2 ? 2 : 0)) + (kCoop ? 3 : (kSplit ? 6 : 0));
   std::atomic<bool>& attr_done = g_attr_set[st.dev][dt_idx][bn_idx][kVariant];
   if (!attr_done.load(std::memory_order_relaxed)) {
     TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     attr_done.store(true, std::memory_order_relaxed);
   }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(tb200::kNumThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n_attr = 0;
   if constexpr (kPair) {
-    // clusters of two CTAs on neighbouring SMs; no multicast is used anywhere in the kernel
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(grid));
-    cfg.blockDim = dim3(tb200::kNumThreads);
-    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tx, tw, to, tr, args));
-  } else {
-    kern<<<grid, tb200::kNumThreads, smem, stream>>>(tx, tw, to, tr, args);
+    // clusters of two CTAs on neighbouring SMs; no multicast load is used anywhere in the kernel
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 2;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
   }
+  if (knobs().pdl != 0) {
+    // programmatic dependent launch: this kernel's prologue (barrier init, TMEM allocation, descriptor prefetch)
+    // may run while the previous kernel on the stream drains; the kernel waits for it before touching global memory
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
+  TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tx, tw, to, tr, args));
   TB_CUDA(cudaGetLastError());
   g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// The K-split kernels exist for the TMA-store / per-lane epilogues only (the host never splits a coop launch).
+template <typename OutT, int BN, bool kPair, bool kRows2, bool kCoop>
+void launch_one(DeviceState& st, int dt_idx, int bn_idx, const CUtensorMap& tx, const CUtensorMap& tw,
+                const CUtensorMap& to, const CUtensorMap& tr, const ConvKernelArgs& args, int grid, int smem,
+                cudaStream_t stream) {
+  if constexpr (!kCoop) {
+    if (args.sk_tiles > 0) {
+      launch_one_variant<OutT, BN, kPair, kRows2, false, true>(st, dt_idx, bn_idx, tx, tw, to, tr, args, grid, smem, stream);
+      return;
+    }
+  }
+  launch_one_variant<OutT, BN, kPair, kRows2, kCoop, false>(st, dt_idx, bn_idx, tx, tw, to, tr, args, grid, smem, stream);
 }
 
 // `coop`: the kernel variant whose epilogue moves its staging boxes to a strided, channel-contiguous output itself.
@@ -395,28 +475,6 @@ CUtensorMapSwizzle tmap_swizzle(int chunk_bytes) {
     case 32: return CU_TENSOR_MAP_SWIZZLE_32B;
     default: return CU_TENSOR_MAP_SWIZZLE_NONE;
   }
-}
-
-int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return (v != nullptr && *v != '\0') ? atoi(v) : dflt;
-}
-
-// Bring-up / test knobs, read from the environment once per process (a getenv per knob per call is a measurable
-// part of the ~6 us a call costs on the host). TRACEA_B200_HOST_CHUNKS is read per call and is not in here.
-struct Knobs {
-  int force_bn, force_stages, force_chunk, no_tma_store, no_tma_residual, tiled_a, force_staging, no_window, prefetch,
-      pair, rows2, panel;
-};
-const Knobs& knobs() {
-  static const Knobs k = {
-      env_int("TRACEA_B200_FORCE_BN", 0),      env_int("TRACEA_B200_FORCE_STAGES", 0),
-      env_int("TRACEA_B200_FORCE_CHUNK", 0),   env_int("TRACEA_B200_NO_TMA_STORE", 0),
-      env_int("TRACEA_B200_NO_TMA_RESIDUAL", 0), env_int("TRACEA_B200_TILED_A", 0),
-      env_int("TRACEA_B200_FORCE_STAGING", 0), env_int("TRACEA_B200_NO_WINDOW", 0),
-      env_int("TRACEA_B200_PREFETCH", 0),      env_int("TRACEA_B200_PAIR", -1),
-      env_int("TRACEA_B200_ROWS2", -1),        env_int("TRACEA_B200_PANEL", 0)};
-  return k;
 }
 
 // ------------------------------------------------------------------ static scratch (no-alloc entry)
@@ -545,6 +603,8 @@ void conv2d_device(int dev, const View4& x_in, const View4& w_in, const View4* b
   if (st.status[0] != 0u) {
     const uint32_t code = st.status[0], blk = st.status[1], det = st.status[2];
     memset(st.status, 0, 4 * sizeof(uint32_t));
+    cudaDeviceSynchronize();
+    reset_split_workspaces(st);
     TB_FAIL(TRACEA_CUDA_ERROR,
             "an earlier conv kernel on device %d gave up a bounded wait (code %u, block %u, detail %u)",
             dev, code, blk, det);
@@ -797,15 +857,6 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   a.total_chunks = static_cast<int>(total_chunks_ll);
   a.C = static_cast<int>(Cg);
   a.a_tiled = a_tiled ? 1 : 0;
-  // L2 prefetch of the activations a few k-steps ahead of the loads: pays only where A streams from HBM with
-  // no reuse and the k-loop is long (1x1 layers with >= 8 k-steps, one column tile, at least two waves: -3 %);
-  // it slows down 3x3 layers and layers whose A is re-read by several column tiles (their A mostly hits L2
-  // already). TRACEA_B200_PREFETCH=n forces a distance, -1 switches it off.
-  a.prefetch_dist = knobs().prefetch > 0 ? knobs().prefetch
-                    : (knobs().prefetch == 0 && R == 1 && S == 1 && total_chunks_ll >= 8 && n_tiles == 1 &&
-                               m_tiles_128 >= 2LL * st.num_sms
-                           ? 4
-                           : 0);
   a.num_n_tiles = static_cast<int>(n_tiles);
   a.b_k0 = static_cast<int>(b_k0);
   a.b_jump_s = static_cast<int>(b_jump_s);
@@ -943,8 +994,77 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     la.shared_bias = shared_bias ? 1 : 0;
     la.idesc = tb200::ptx::make_idesc(fmt, pair_v ? 2 * tb200::kBlockM : tb200::kBlockM, bn);
     const long long tiles = m_tiles * n_tiles;
-    const int grid = pair_v ? 2 * static_cast<int>(std::min<long long>(tiles, st.num_sms / 2))
-                            : static_cast<int>(std::min<long long>(tiles, st.num_sms));
+    const long long workers_max = pair_v ? st.num_sms / 2 : st.num_sms;   // CTAs, or CTA pairs
+    long long workers = std::min<long long>(tiles, workers_max);
+
+    // ---- work schedule. A layer whose tile count is not a multiple of the worker count leaves SMs idle in its
+    // last wave; a layer with fewer tiles than SMs leaves them idle throughout. Cutting tiles over K evens that
+    // out: the k-steps of a "split region" of tiles are laid end to end and dealt out in equal shares, so that
+    // several workers compute one tile, each over a slice of K, and exchange fp32 partial sums through scratch
+    // memory (the piece that finishes last adds them up and runs the epilogue).
+    //  * more than one wave: the split region is the partial wave plus one whole wave, so every share is longer
+    //    than one tile and no tile is cut into more than two pieces; the waves before it stay whole tiles;
+    //  * less than one wave: every tile is in the region, shares of at least four k-steps.
+    // OFF unless TRACEA_B200_SPLIT_K=1 (2: also when it saves a single k-step). Measured on B200 it loses: a
+    // 256 x 256 fp32 partial sum is as many bytes as the operands of four k-steps, and these kernels already run at
+    // the rate L2 can feed the SMs, so the exchange costs more than the idle tail it removes (1x1 1024->256 at
+    // 256 images: 31 -> 55 us; 3x3 256->256: 46 -> 61 us; 3x3 512->512 at 64 images: 27 -> 31 us). Kept as a
+    // tested option for parts with a different balance. 128-byte k-chunks only.
+    la.dp_tiles = static_cast<int>(tiles);
+    Scratch sk_scratch;
+    const long long k_iters = total_chunks_ll;   // 128-byte chunks: one per pipeline stage
+    const int split_env = knobs().split_k;
+    if (chunk_bytes == 128 && !a_tiled && !coop && split_env != 0 && arena == nullptr && k_iters >= 2 &&
+        2 * workers_max * k_iters < (1LL << 30)) {
+      const long long rem = tiles % workers_max;       // tiles of the last, partly filled wave (all of them if < 1 wave)
+      if (rem > 0) {
+        long long region = 0, sk_workers = 0, saved = 0, min_saved = 0;
+        if (tiles > workers_max) {
+          region = rem + workers_max;
+          sk_workers = workers_max;
+          saved = 2 * k_iters - (region * k_iters + sk_workers - 1) / sk_workers;
+          min_saved = split_env == 2 ? 1 : 4;
+        } else {
+          const long long min_share = split_env == 2 ? 1 : 4;
+          region = rem;
+          sk_workers = std::min<long long>(workers_max, rem * k_iters / min_share);
+          saved = sk_workers > rem ? k_iters - (region * k_iters + sk_workers - 1) / sk_workers : 0;
+          min_saved = split_env == 2 ? 1 : 8;
+        }
+        {
+          const long long rem = region;   // the tiles of the split region
+          if (saved >= min_saved) {
+            la.sk_slot_floats = 256LL * bn;
+            const size_t partial_bytes = static_cast<size_t>(2 * sk_workers * la.sk_slot_floats) * sizeof(float);
+            const size_t counter_bytes = static_cast<size_t>(rem) * 8 * 2 * sizeof(uint32_t);
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) {
+              cudaGetLastError();   // e.g. another thread is capturing in global mode: run this call unsplit
+              cap = cudaStreamCaptureStatusInvalidated;
+            }
+            // a graph may be replayed at any time, next to anything: it never shares a stream's block
+            void* ws = cap == cudaStreamCaptureStatusNone ? split_workspace(st, stream) : nullptr;
+            if (ws != nullptr) {
+              la.sk_partials = static_cast<float*>(ws);
+              la.sk_counters = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + st.split_partial_bytes);
+            } else if (cap == cudaStreamCaptureStatusActive) {
+              // inside a graph capture on a stream without a block: memory the graph owns, cleared by a memset node
+              sk_scratch.alloc(st, partial_bytes + counter_bytes, stream);
+              la.sk_partials = static_cast<float*>(sk_scratch.ptr);
+              la.sk_counters = reinterpret_cast<uint32_t*>(static_cast<char*>(sk_scratch.ptr) + partial_bytes);
+              TB_CUDA(cudaMemsetAsync(la.sk_counters, 0, counter_bytes, stream));
+            }
+            if (la.sk_partials != nullptr) {
+              la.sk_tiles = static_cast<int>(rem);
+              la.dp_tiles = static_cast<int>(tiles - rem);
+              la.sk_workers = static_cast<int>(sk_workers);
+              workers = tiles >= workers_max ? workers_max : sk_workers;
+            }
+          }
+        }
+      }
+    }
+    const int grid = static_cast<int>(pair_v ? 2 * workers : workers);
     switch (x.dtype) {
       case TRACEA_DTYPE_BFLOAT16:
         launch_bn<__nv_bfloat16>(st, 0, bn, pair_v, rows2_v, coop, tmap_x, tmap_w, tmap_out, tmap_res, la, grid, smem, stream);
@@ -1645,6 +1765,11 @@ void tracea_shutdown(void) {
     }
     if (st.pool != nullptr) cudaMemPoolDestroy(st.pool);
     if (st.status != nullptr) cudaFreeHost(st.status);
+    {
+      std::lock_guard<std::mutex> ws_lock(st.ws_mu);
+      for (auto& kv : st.split_ws) cudaFree(kv.second);
+      st.split_ws.clear();
+    }
     st.pool = nullptr;
     st.status = nullptr;
     st.copy_in = st.copy_out = nullptr;
