@@ -265,6 +265,11 @@ int32_t tracea_b200_pool_stats(int32_t device_id, uint64_t stats[4], int32_t res
  * convolution). Benchmarks read it before and after a timed region. No counterpart in the reference. */
 uint64_t tracea_b200_launch_count(void);
 
+/* The same count for one kind of kernel: 0 the general implicit-GEMM conv kernel, 1 its instantiations that cut tiles
+ * over K, 2 the resident-filter kernel (stride-1 small filters over 64-channel activations), 3 layout adapters.
+ * Lets tests and benchmarks see which path a call took. 0 for any other `kind`. No counterpart in the reference. */
+uint64_t tracea_b200_launch_count_of(int32_t kind);
+
 #ifdef __cplusplus
 }
 #endif

@@ -568,3 +568,54 @@ def test_tiles_split_over_k_match_the_oracle_and_repeat_bit_for_bit():
     res = subprocess.run([sys.executable, "-c", _SPLIT_K_SCRIPT, root], env=env, capture_output=True, text=True,
                          timeout=600)
     assert res.returncode == 0 and "split-k ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+# --------------------------------------------------------------------------- resident-filter kernel (stride-1 small filters, C = 64)
+RESIDENT = [
+    # N, H, W, K, R, S, pad, dtype, epilogue
+    (32, 56, 56, 64, 3, 3, 1, "bf16", "bias+relu"),      # the reference's benchmark layer at batch 32: full + short tiles
+    (33, 56, 56, 64, 3, 3, 1, "bf16", "bias+relu"),      # odd tile counts: one CTA of the last pair has no tile
+    (40, 56, 56, 40, 3, 3, 1, "f16", "bias+silu"),       # K_out < 64: zero filter rows, masked stores
+    (64, 40, 31, 64, 3, 3, 1, "bf16", ""),               # odd width, no bias
+    (64, 40, 31, 64, 3, 3, 0, "bf16", "bias"),           # no padding: the dummy columns are real input columns
+    (64, 30, 50, 64, 2, 3, (1, 1), "bf16", "gelu"),      # 2x3 filter, one output row more than input rows
+    (200, 28, 28, 64, 3, 3, 1, "bf16", "relu"),
+    (150, 20, 120, 48, 3, 3, (0, 1), "f16", "bias+relu"),   # wide rows: three-block tiles, no short tile
+]
+
+
+@pytest.mark.parametrize("case", RESIDENT, ids=lambda c: "N%dH%dW%dK%dR%dS%d" % c[:6])
+def test_resident_filter_kernel_matches_the_oracle(case):
+    """Stride-1 small filters over 64-channel 16-bit activations take the kernel that keeps the filter bank in
+    shared memory and reads every tap from one halo'd window (conv2d_window_sm100.cuh): full tensors against the
+    oracle, and the launch counter shows that this kernel -- not the general one -- produced them."""
+    N, H, W, K, R, S, pad, dtype, epi = case
+    x = cc.normal((N, 64, H, W), 6, "rf/x")
+    w = cc.kaiming((K, 64, R, S), 6, "rf/w")
+    b = cc.normal((K,), 6, "rf/b", 0.1)
+    before = ffi.launch_count_of(ffi.KERNEL_RESIDENT_FILTER)
+    check(x, w, b, None, 1, pad, 1, epi, dtype)
+    assert ffi.launch_count_of(ffi.KERNEL_RESIDENT_FILTER) == before + 1
+
+
+def test_resident_filter_kernel_writes_strided_views_and_agrees_with_the_general_kernel():
+    """Output as a channel slice of a wider buffer (pixel pitch 96): the gaps keep their contents; and the general
+    kernel (smaller batch, same images) gives the same values up to the summation order inside an MMA."""
+    n = 40
+    x = cc.normal((n, 64, 56, 56), 7, "rf2/x")
+    w = cc.kaiming((64, 64, 3, 3), 7, "rf2/w")
+    b = cc.normal((64,), 7, "rf2/b", 0.1)
+    tx, tw, tb = to_dev(x, "bf16"), to_dev(w, "bf16"), torch.from_numpy(b).cuda()
+    big = torch.full((n, 96, 56, 56), 7.0, dtype=torch.bfloat16, device="cuda").contiguous(memory_format=torch.channels_last)
+    view = big[:, 16:80]
+    before = ffi.launch_count_of(ffi.KERNEL_RESIDENT_FILTER)
+    ops.conv2d_into(tx, tw, view, tb, None, 1, 1, 1, 1, ffi.EPILOGUE_BIAS_RELU)
+    torch.cuda.synchronize()
+    assert ffi.launch_count_of(ffi.KERNEL_RESIDENT_FILTER) == before + 1
+    assert (big[:, :16] == 7.0).all() and (big[:, 80:] == 7.0).all()
+    general = ops.conv2d_nchw(tx[:2], tw, tb, None, 1, 1, 1, 1, "bias+relu")     # 2 images: too few tiles, general kernel
+    assert ffi.launch_count_of(ffi.KERNEL_RESIDENT_FILTER) == before + 1
+    a, g = view[:2].float(), general.float()
+    assert float((a - g).abs().max()) <= 2.0 ** -7 * float(g.abs().max())
+    want = run_oracle(x, w, b, None, 1, 1, 1, "bias+relu", "bf16")
+    assert cc.rel_err(view.float().cpu().numpy(), want) <= cc.TOL_16BIT

@@ -160,14 +160,19 @@ __device__ __forceinline__ void apply_act32(float (&f)[32], int act) {
   }
 }
 
-__device__ __forceinline__ void report_error(const ConvKernelArgs& a, volatile uint32_t* abort_flag,
-                                             uint32_t code, uint32_t detail) {
+// Records the first error of the device in `status` ({code, block, detail, 0}) and raises the CTA's abort flag.
+__device__ __forceinline__ void report_error_status(uint32_t* status, volatile uint32_t* abort_flag, uint32_t code,
+                                                    uint32_t detail) {
   *abort_flag = 1u;
-  if (a.status != nullptr && atomicCAS(a.status, 0u, code) == 0u) {
-    a.status[1] = blockIdx.x;
-    a.status[2] = detail;
+  if (status != nullptr && atomicCAS(status, 0u, code) == 0u) {
+    status[1] = blockIdx.x;
+    status[2] = detail;
     __threadfence_system();
   }
+}
+__device__ __forceinline__ void report_error(const ConvKernelArgs& a, volatile uint32_t* abort_flag,
+                                             uint32_t code, uint32_t detail) {
+  report_error_status(a.status, abort_flag, code, detail);
 }
 
 // Shared memory map (offsets from a 1024-byte aligned base):

@@ -24,6 +24,7 @@
 
 #include "../../include/tracea_b200.h"
 #include "conv2d_sm100.cuh"
+#include "conv2d_window_sm100.cuh"
 #include "layout_kernels.cuh"
 
 namespace {
@@ -103,6 +104,8 @@ DeviceState g_dev[kMaxDevices];
 // Setting the attribute twice is harmless, so a relaxed flag is enough.
 std::atomic<bool> g_attr_set[kMaxDevices][3][3][9];
 std::atomic<unsigned long long> g_kernel_launches{0};   // every kernel this library has launched (conv + layout adapters)
+// the same, by kind: 0 general implicit-GEMM kernel, 1 its K-split instantiations, 2 resident-filter kernel, 3 layout adapters
+std::atomic<unsigned long long> g_launches_by_kind[4];
 EncodeTiledFn g_encode_tiled = nullptr;
 EncodeIm2colFn g_encode_im2col = nullptr;
 
@@ -332,7 +335,7 @@ int env_int(const char* name, int dflt) {
 // part of the ~6 us a call costs on the host). TRACEA_B200_HOST_CHUNKS is read per call and is not in here.
 struct Knobs {
   int force_bn, force_stages, force_chunk, no_tma_store, no_tma_residual, tiled_a, force_staging, no_window,
-      pair, rows2, panel, pdl, split_k;
+      pair, rows2, panel, pdl, split_k, no_window3;
 };
 const Knobs& knobs() {
   static const Knobs k = {
@@ -342,7 +345,7 @@ const Knobs& knobs() {
       env_int("TRACEA_B200_FORCE_STAGING", 0), env_int("TRACEA_B200_NO_WINDOW", 0),
       env_int("TRACEA_B200_PAIR", -1),         env_int("TRACEA_B200_ROWS2", -1),
       env_int("TRACEA_B200_PANEL", 0),         env_int("TRACEA_B200_PDL", 1),
-      env_int("TRACEA_B200_SPLIT_K", 0)};
+      env_int("TRACEA_B200_SPLIT_K", 0),       env_int("TRACEA_B200_NO_RESIDENT_FILTER", 0)};
   return k;
 }
 
@@ -414,6 +417,7 @@ void launch_one_variant(DeviceState& st, int dt_idx, int bn_idx, const CUtensorM
   TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tx, tw, to, tr, args));
   TB_CUDA(cudaGetLastError());
   g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  g_launches_by_kind[kSplit ? 1 : 0].fetch_add(1, std::memory_order_relaxed);
 }
 
 // The K-split kernels exist for the TMA-store / per-lane epilogues only (the host never splits a coop launch).
@@ -576,6 +580,7 @@ void launch_weight_pack(const void* src, void* dst, int es, long long K, long lo
   }
   TB_CUDA(cudaGetLastError());
   g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  g_launches_by_kind[3].fetch_add(1, std::memory_order_relaxed);
 }
 
 
@@ -629,6 +634,142 @@ void conv2d_device_noalloc(int dev, const View4& x_in, const View4& w_in, const 
   arena.base = na.scratch;
   arena.capacity = kStaticScratchBytes;
   conv2d_core(st, &arena, x_in, w_in, bias, residual, out, p, epi);
+}
+
+// ------------------------------------------------------------------ resident-filter kernel (stride-1 small filters, C = 64)
+// Tries the kernel of conv2d_window_sm100.cuh: filter bank resident in shared memory, one halo'd window copy per
+// tile, filter taps as shifted descriptors over the window. `x` is channels-last with 64 channels, `w_ptr` dense
+// [K][R][S][64]. Returns false (nothing launched) when the layer does not qualify.
+std::atomic<bool> g_window_attr_set[kMaxDevices][2];
+
+bool try_resident_filter_conv(DeviceState& st, const View4& x, const void* w_ptr, const View4* bias, const View4& out,
+                              const CoreParams& p, const Epilogue& epi, long long K, long long R, long long S,
+                              bool out_vec, cudaStream_t stream) {
+  const long long N = x.shape[0], H = x.shape[2], W = x.shape[3];
+  const long long Ho = out.shape[2], Wo = out.shape[3];
+  if (knobs().no_window3 != 0 || x.dtype == TRACEA_DTYPE_FLOAT32 || x.shape[1] != 64 || K > 64 || (K % 8) != 0) return false;
+  if (p.stride_h != 1 || p.stride_w != 1 || p.dilation_h != 1 || p.dilation_w != 1) return false;
+  if (R > 3 || S > 3 || R * S < 4 || !out_vec || (epi.residual)) return false;
+  if (p.pad_w_hi > (long long)p.padding_w || W + p.padding_w > 256 || N > 0x3fffffffLL / (Ho + 1)) return false;
+  const long long Wp = W + p.padding_w, dummy = Wp - Wo;
+  if (dummy < 0) return false;
+  const uint32_t w_bytes = static_cast<uint32_t>(R * S) * 4096u;
+  long long ht = 0, nblk = 0, slot_bytes = 0, box_rows = 0;
+  for (long long nb = tb200::kWinMaxBlocks; nb >= 1; --nb) {
+    long long h = std::min<long long>((128 * nb + dummy) / Wp, Ho);
+    if (h < 1 || h + R - 1 > 256) continue;
+    const long long rows = (h + R - 1) * Wp;                            // what a window copy fills
+    const long long reach = 128 * nb + (R - 1) * Wp + (S - 1);         // what the MMAs of nb blocks read
+    const long long slot = (std::max(rows + p.pad_w_hi, reach) * 128 + 1023) / 1024 * 1024;
+    if (tb200::window_smem_bytes(w_bytes, static_cast<uint32_t>(slot)) > 232448u) continue;
+    ht = h; nblk = nb; slot_bytes = slot; box_rows = rows;
+    break;
+  }
+  if (ht == 0) return false;
+  const long long nblk_full = (ht * Wp - dummy + 127) / 128;
+  const long long tiles_per_img = Ho / ht, ht_short = Ho % ht;
+  const long long nblk_short = ht_short > 0 ? (ht_short * Wp - dummy + 127) / 128 : 0;
+  // worth it only when the 128-row MMA blocks are mostly real pixels and the launch fills the GPU at least once
+  const long long blocks_per_img = tiles_per_img * nblk_full + nblk_short;
+  if (Ho * Wo * 100 < blocks_per_img * 128 * 85) return false;
+  const long long n_full = N * tiles_per_img, n_short = ht_short > 0 ? N : 0;
+  const long long pair_full = (n_full + 1) / 2, pair_tiles = pair_full + (n_short + 1) / 2;
+  if (pair_tiles < st.num_sms / 2 || pair_tiles > 0x3fffffffLL) return false;
+  (void)nblk;
+
+  auto encode_x = [&](CUtensorMap* m, long long box_h) {
+    const int es = 2;
+    const cuuint64_t gdim[4] = {64, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    const cuuint64_t gstr[3] = {(cuuint64_t)(x.stride[3] * es), (cuuint64_t)(x.stride[2] * es),
+                                (cuuint64_t)(x.stride[0] * es)};
+    const cuuint32_t box[4] = {64u, (cuuint32_t)Wp, (cuuint32_t)box_h, 1u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = g_encode_tiled(m, tmap_dtype(x.dtype), 4, x.ptr, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled (window) failed with %d", (int)r);
+  };
+  CUtensorMap tmap_full, tmap_short, tmap_w;
+  encode_x(&tmap_full, ht + R - 1);
+  // a short tile's copy takes one row more than it needs: the right-hand padding of its last row reads there
+  // (below a full tile's copy the slot is kept zero instead)
+  encode_x(&tmap_short, ht_short > 0 ? ht_short + R : ht + R - 1);
+  {
+    const cuuint64_t gdim[2] = {(cuuint64_t)(R * S * 64), (cuuint64_t)K};
+    const cuuint64_t gstr[1] = {(cuuint64_t)(R * S * 64 * 2)};
+    const cuuint32_t box[2] = {64u, 32u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = g_encode_tiled(&tmap_w, tmap_dtype(x.dtype), 2, const_cast<void*>(w_ptr), gdim, gstr, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled (filter bank) failed with %d", (int)r);
+  }
+
+  tb200::WindowKernelArgs a;
+  memset(&a, 0, sizeof(a));
+  a.R = (int)R; a.S = (int)S; a.pad_h = (int)p.padding_h; a.pad_w = (int)p.padding_w;
+  a.Wp = (int)Wp; a.Ho = (int)Ho; a.Wo = (int)Wo;
+  a.ht_full = (int)ht; a.nblk_full = (int)nblk_full; a.ht_short = (int)ht_short; a.nblk_short = (int)nblk_short;
+  a.tiles_per_img = (int)tiles_per_img; a.n_full = (int)n_full; a.n_short = (int)n_short;
+  a.pair_tiles_full = (int)pair_full; a.pair_tiles = (int)pair_tiles;
+  a.box_bytes_full = static_cast<uint32_t>(box_rows * 128);
+  a.box_bytes_short = static_cast<uint32_t>((ht_short > 0 ? ht_short + R : ht + R - 1) * Wp * 128);
+  a.w_bytes = w_bytes;
+  a.slot_bytes = static_cast<uint32_t>(slot_bytes);
+  a.zero_from = a.box_bytes_full;
+  a.idesc = tb200::ptx::make_idesc(x.dtype == TRACEA_DTYPE_FLOAT16 ? 0u : 1u, 256, tb200::kWinBN);
+  a.K_out = (int)K;
+  a.out = out.ptr;
+  a.out_sn = out.stride[0]; a.out_sh = out.stride[2]; a.out_sw = out.stride[3];
+  if (epi.bias && bias != nullptr) {
+    a.bias = bias->ptr;
+    a.bias_is_f32 = bias->dtype == TRACEA_DTYPE_FLOAT32 ? 1 : 0;
+  }
+  a.act = epi.act;
+  a.status = st.status;
+#ifdef TB200_PROFILE
+  {
+    const char* pp = getenv("TRACEA_B200_PROF_PTR");
+    a.prof = pp != nullptr ? reinterpret_cast<long long*>(strtoull(pp, nullptr, 0)) : nullptr;
+  }
+#endif
+
+  const int smem = static_cast<int>(tb200::window_smem_bytes(w_bytes, a.slot_bytes));
+  const int grid = 2 * static_cast<int>(std::min<long long>(pair_tiles, st.num_sms / 2));
+  const bool bf16 = x.dtype == TRACEA_DTYPE_BFLOAT16;
+  auto kern_bf = tb200::conv2d_window_sm100_kernel<__nv_bfloat16>;
+  auto kern_h = tb200::conv2d_window_sm100_kernel<__half>;
+  std::atomic<bool>& attr_done = g_window_attr_set[st.dev][bf16 ? 0 : 1];
+  if (!attr_done.load(std::memory_order_relaxed)) {
+    if (bf16) TB_CUDA(cudaFuncSetAttribute(kern_bf, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    else TB_CUDA(cudaFuncSetAttribute(kern_h, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    attr_done.store(true, std::memory_order_relaxed);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(tb200::kWinThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n_attr = 0;
+  attr[n_attr].id = cudaLaunchAttributeClusterDimension;   // CTA pairs; no multicast load anywhere in the kernel
+  attr[n_attr].val.clusterDim.x = 2;
+  attr[n_attr].val.clusterDim.y = 1;
+  attr[n_attr].val.clusterDim.z = 1;
+  ++n_attr;
+  if (knobs().pdl != 0) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
+  if (bf16) TB_CUDA(cudaLaunchKernelEx(&cfg, kern_bf, tmap_full, tmap_short, tmap_w, a));
+  else TB_CUDA(cudaLaunchKernelEx(&cfg, kern_h, tmap_full, tmap_short, tmap_w, a));
+  TB_CUDA(cudaGetLastError());
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  g_launches_by_kind[2].fetch_add(1, std::memory_order_relaxed);
+  return true;
 }
 
 void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const View4& w_in, const View4* bias,
@@ -686,6 +827,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
           (int)p.padding_w, pixels, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
     TB_CUDA(cudaGetLastError());
     g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    g_launches_by_kind[3].fetch_add(1, std::memory_order_relaxed);
     x.ptr = x_stage;
     x.stride[0] = H * Wpitch * Cp;
     x.stride[1] = 1;
@@ -708,6 +850,7 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
           (int)W, (int)Cp, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
     TB_CUDA(cudaGetLastError());
     g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    g_launches_by_kind[3].fetch_add(1, std::memory_order_relaxed);
     x.ptr = x_stage;
     x.stride[0] = H * W * Cp;
     x.stride[1] = 1;
@@ -772,6 +915,15 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   }
 
   const long long Kgemm = R * Sg * Cg;
+
+  // ---- stride-1 small filters over 64-channel activations: the resident-filter kernel, when the layer qualifies
+  {
+    const bool ovec = (out.stride[1] == 1) && aligned16(out.ptr) && (out.stride[0] * es) % 16 == 0 &&
+                      (out.stride[2] * es) % 16 == 0 && (out.stride[3] * es) % 16 == 0 && (K % vec_elems) == 0;
+    if (!window && !w_remap && Cp == 64 && C == 64 && st.status != nullptr &&
+        try_resident_filter_conv(st, x, w_ptr, bias, out, p, epi, K, R, S, ovec, stream))
+      return;
+  }
 
   // ---- tiling of the whole problem
   const long long m_tiles_128 = (M + tb200::kBlockM - 1) / tb200::kBlockM;
@@ -1793,6 +1945,11 @@ int32_t tracea_b200_conv_transpose_plan(uint32_t in_extent, uint32_t out_extent,
 }
 
 uint64_t tracea_b200_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
+
+uint64_t tracea_b200_launch_count_of(int32_t kind) {
+  if (kind < 0 || kind >= 4) return 0;
+  return g_launches_by_kind[kind].load(std::memory_order_relaxed);
+}
 
 uint32_t tracea_b200_device_status(int32_t device_id) {
   if (device_id < 0 || device_id >= kMaxDevices) return 0;

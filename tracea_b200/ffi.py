@@ -24,7 +24,7 @@ DTYPE_FLOAT32, DTYPE_FLOAT16, DTYPE_BFLOAT16, DTYPE_INT32, DTYPE_INT8 = 0, 1, 2,
 EXPORTED_SYMBOLS = (
     "tracea_conv2d", "tracea_conv2d_v0", "tracea_conv2d_noalloc", "tracea_get_last_error", "tracea_clear_error",
     "tracea_version_major", "tracea_version_minor", "tracea_version_patch", "tracea_init",
-    "tracea_shutdown", "tracea_b200_device_status", "tracea_b200_launch_count", "tracea_b200_pool_stats",
+    "tracea_shutdown", "tracea_b200_device_status", "tracea_b200_launch_count", "tracea_b200_launch_count_of", "tracea_b200_pool_stats",
     "tracea_b200_conv_transpose_plan",
     "tracea_gemm", "tracea_conv_transpose2d", "tracea_conv2d_prepack_bytes", "tracea_conv2d_prepack",
     "tracea_gemm_prepack_b_bytes", "tracea_gemm_prepack_b",
@@ -124,6 +124,8 @@ def load():
     lib.tracea_b200_device_status.restype = ctypes.c_uint32
     lib.tracea_b200_pool_stats.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_uint64), ctypes.c_int32]
     lib.tracea_b200_pool_stats.restype = ctypes.c_int32
+    lib.tracea_b200_launch_count_of.argtypes = [ctypes.c_int32]
+    lib.tracea_b200_launch_count_of.restype = ctypes.c_uint64
     lib.tracea_b200_launch_count.argtypes = []
     lib.tracea_b200_launch_count.restype = ctypes.c_uint64
     lib.tracea_b200_conv_transpose_plan.argtypes = [ctypes.c_uint32] * 5 + [ctypes.POINTER(ctypes.c_int64)]
@@ -211,6 +213,14 @@ def conv_transpose2d_raw(x, w, bias, residual, out, stride=(1, 1), padding=(0, 0
     if check and st != SUCCESS:
         raise TraceaError(st, last_error(), "tracea_conv_transpose2d")
     return st
+
+
+KERNEL_GENERAL, KERNEL_SPLIT_K, KERNEL_RESIDENT_FILTER, KERNEL_LAYOUT = range(4)
+
+
+def launch_count_of(kind):
+    """Launches so far of one kind of kernel (KERNEL_* above)."""
+    return int(load().tracea_b200_launch_count_of(kind))
 
 
 def pool_stats(device_id=0, reset_high=False):
