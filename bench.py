@@ -14,9 +14,15 @@ The batch is sharded by image across GPUs with no collective on the data path (w
 
 One JSON line is printed by rank 0. `value` is TFLOP/s over all GPUs with the reference's FLOP
 convention 2*M*K_out*(C*R*S) (src/optimizer/benchmark.rs:458-469). `e2e` is the same metric through
-the C ABI with HOST (pinned) tensors, i.e. with the host<->device copies inside the timed region.
-`roofline` is for the dominant kernel, the 3x3 conv. `cpu_baseline` times the CPU restatement of the
-reference's SIMD conv path on the host cores (N=1 GPU runs only). `--impl reference` times only that.
+the C ABI with HOST (pinned) tensors, one tracea_conv2d call per layer, i.e. with every tensor of every
+call crossing the bus inside the timed region; `e2e_graph` runs the same block as a fused graph from
+host memory (input copied in once, intermediates stay on the device, one output copied back).
+`roofline` is for the dominant kernel, the 3x3 conv. `configs` times the other benchmark configurations
+(one fp32 NCHW call, the fp16 README shape, the strided bf16 downsample, the reference's own 3x3 64->64
+layer at its batch sizes), `resnet50` the 53-conv stack with a table per layer shape. `cpu_baseline`
+times the reference's CPU conv path on the host cores (N=1 GPU runs only): what its Python op executes
+on CPU tensors (torch.nn.functional.conv2d, tracea-python/src/conv2d.rs:80-136), next to the CPU
+restatement of its SIMD GEMM engine fed by im2col and the scalar loop. `--impl reference` times only those.
 """
 import argparse
 import json
@@ -33,10 +39,11 @@ BATCH_PER_GPU = 256
 L2_BYTES = 126 * 1024 * 1024
 WORKLOAD = ("resnet50_stage3_bottleneck_bf16: 1x1 1024->256 +bias+relu, 3x3 256->256 p1 +bias+relu, "
             "1x1 256->1024 +bias+residual+relu @14x14, %d images per GPU" % BATCH_PER_GPU)
-# dram__bytes_read.sum + dram__bytes_write.sum of one 3x3-conv launch at N=256, from the ncu capture
-# summarised in profiles/conv3x3_c256_k256_n256_bf16.md (26.95 MB read + 0.02 MB written; the 25.7 MB
-# output is still dirty in L2 when the launch ends, which is why this is below the algorithmic bytes).
+# dram__bytes_read.sum + dram__bytes_write.sum of one 3x3-conv launch at N=256: NOT measured by this run but taken
+# from the ncu capture summarised in profiles/conv3x3_c256_k256_n256_bf16.md (26.95 MB read + 0.02 MB written; the
+# 25.7 MB output is still dirty in L2 when the launch ends, which is why this is below the algorithmic bytes).
 CONV3X3_NCU_TRAFFIC_BYTES = 26967552
+CONV3X3_NCU_TRAFFIC_SOURCE = "static: one ncu capture of this kernel at 256 images, profiles/conv3x3_c256_k256_n256_bf16.md"
 
 
 def load_peaks():
@@ -127,6 +134,7 @@ def block_flops(n_images):
 
 
 def time_cpu_baseline(n_images, steps, warmup, budget_s=None):
+    """B2: the oracle's im2col + packed AVX2/FMA GEMM path (restatement of src/kernels/cpu/gemm.rs), all cores."""
     from oracle import oracle
     threads = os.cpu_count() or 1
     x, ws, bs = block_oracle_inputs(n_images)
@@ -143,6 +151,78 @@ def time_cpu_baseline(n_images, steps, warmup, budget_s=None):
     return block_flops(n_images) * done / dt / 1e12, dt / done * 1e3, threads, done
 
 
+def time_cpu_torch(n_images, steps, warmup, budget_s=None):
+    """B1: what the reference's conv op executes on CPU tensors -- torch.nn.functional.conv2d in fp32
+    (tracea-python/src/conv2d.rs:80-136 falls back to it; its dtype guard forces fp32), bias / residual / ReLU as
+    separate torch ops, all cores."""
+    import torch
+    import torch.nn.functional as F
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    x, ws, bs = block_oracle_inputs(n_images)
+    tx = torch.from_numpy(x.copy()).contiguous(memory_format=torch.channels_last)
+    tws = [torch.from_numpy(w).contiguous(memory_format=torch.channels_last) for w in ws]
+    tbs = [torch.from_numpy(b) for b in bs]
+
+    def step():
+        with torch.no_grad():
+            y1 = F.relu(F.conv2d(tx, tws[0], tbs[0]))
+            y2 = F.relu(F.conv2d(y1, tws[1], tbs[1], 1, 1))
+            return F.relu(F.conv2d(y2, tws[2], tbs[2]) + tx)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        step()
+        done += 1
+        if budget_s is not None and time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return block_flops(n_images) * done / dt / 1e12, dt / done * 1e3, threads, done
+
+
+def time_cpu_scalar_config1(budget_s=4.0):
+    """B0: the scalar restatement of cpu_conv2d (examples/verify_conv2d.rs:8-44) on benchmark configuration 1
+    (fp32 x[1,64,56,56] * w[64,64,3,3] + bias, ReLU), one thread."""
+    import numpy as np
+    from oracle import oracle
+    rng = np.random.default_rng(0)
+    x = rng.uniform(-1, 1, (1, 64, 56, 56)).astype(np.float32)
+    w = rng.uniform(-1, 1, (64, 64, 3, 3)).astype(np.float32)
+    b = (rng.standard_normal(64) * 0.1).astype(np.float32)
+    oracle.conv2d(x, w, b, None, 1, 1, 1, "relu")
+    t0 = time.perf_counter()
+    done = 0
+    while done < 20 and time.perf_counter() - t0 < budget_s:
+        oracle.conv2d(x, w, b, None, 1, 1, 1, "relu")
+        done += 1
+    dt = (time.perf_counter() - t0) / done
+    return 2.0 * 56 * 56 * 64 * 64 * 9 / dt / 1e12, dt * 1e3, done
+
+
+def cpu_baselines(n_images, budget_s):
+    """The three CPU baselines of the reference's conv path, each on a bounded sample. The headline one is B1: it
+    is literally the code the reference runs for this op on CPU tensors."""
+    tf1, ms1, threads, done1 = time_cpu_torch(n_images, 1000, 1, budget_s=budget_s)
+    tf2, ms2, _, done2 = time_cpu_baseline(n_images, 1000, 1, budget_s=budget_s)
+    tf0, ms0, done0 = time_cpu_scalar_config1()
+    main = {"value": tf1, "unit": "TFLOP/s", "cores": threads, "kind": "reference",
+            "sample": "bottleneck block on %d of the 256 images, fp32, %d passes (%.0f ms each): "
+                      "torch.nn.functional.conv2d on CPU tensors, the call the reference's conv op makes on CPU "
+                      "(tracea-python/src/conv2d.rs:80-136)" % (n_images, done1, ms1)}
+    others = {
+        "simd_gemm_port": {"value": tf2, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                           "sample": "same block and sample, %d passes (%.0f ms each): im2col + packed AVX2/FMA GEMM "
+                                     "restatement of the reference's CPU engine (src/kernels/cpu/gemm.rs)" % (done2, ms2)},
+        "scalar_config1": {"value": tf0, "unit": "TFLOP/s", "cores": 1, "kind": "port",
+                           "sample": "benchmark configuration 1 (fp32 x[1,64,56,56], 3x3 64->64, bias+ReLU), %d passes "
+                                     "(%.0f ms each): scalar restatement of examples/verify_conv2d.rs:8-44" % (done0, ms0)},
+    }
+    return main, others
+
+
 def run_reference(args):
     """The reference's CPU conv path (no CUDA anywhere): rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
@@ -150,16 +230,21 @@ def run_reference(args):
         return
     n_sample = 8
     warm = max(1, min(args.warmup, 3))
-    tflops, ms, threads, done = time_cpu_baseline(n_sample, args.steps, warm, budget_s=150.0)
+    tflops, ms, threads, done = time_cpu_torch(n_sample, args.steps, warm, budget_s=100.0)
+    tf2, ms2, _, done2 = time_cpu_baseline(n_sample, args.steps, warm, budget_s=40.0)
     line = {
         "impl": "reference", "metric": "conv2d_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": done, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "sample": "%d images per step (of 256)" % n_sample},
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                         "sample": "bottleneck block on %d images per step, fp32, im2col + packed AVX2/FMA GEMM "
-                                   "restatement of the reference's CPU engine (the reference is Rust and cannot "
-                                   "be built here)" % n_sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "reference",
+                         "sample": "bottleneck block on %d images per step, fp32: torch.nn.functional.conv2d on CPU "
+                                   "tensors, the call the reference's conv op makes on CPU (tracea-python/src/conv2d.rs:"
+                                   "80-136; the reference's Rust kernels cannot be built here and it has no CPU conv "
+                                   "kernel of its own)" % n_sample},
+        "cpu_baseline_simd_gemm_port": {"value": tf2, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                        "sample": "same block, %d passes of %.0f ms: im2col + packed AVX2/FMA GEMM "
+                                                  "restatement of src/kernels/cpu/gemm.rs" % (done2, ms2)},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -179,7 +264,7 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's own log lines, if asked for, stay off stdout
         dist.init_process_group("nccl", device_id=dev)
     if rank == 0:
         build.build()
@@ -211,44 +296,46 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize(dev)
 
-    if args.only_layer is not None:
-        # profiling aid: launch one layer of the block a few times and exit (no JSON line)
-        j = [sp.name.split(".")[-1] for sp in specs].index(args.only_layer)
-        for i in range(warmup + steps):
-            stacks[i % n_sets].launch_one(j)
-        barrier()
-        print("launched %s %d times" % (specs[j].name, warmup + steps), flush=True)
-        return
-
     for i in range(warmup):
         stacks[i % n_sets].forward()
     barrier()
 
-    # ---- timed region: K steps, device-timed; an event between launches gives per-layer durations
+    # ---- timed region: exactly K steps back to back, one event before and one after (consecutive launches overlap
+    # their prologues with the previous kernel's tail: programmatic dependent launch, which any event in between
+    # would switch off)
     nl = len(specs)
-    events = [torch.cuda.Event(enable_timing=True) for _ in range(steps * nl + 1)]
+    e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = lib.tracea_b200_launch_count()
     with ClockSampler(local_rank) as clocks:
-        events[0].record(stream)
+        e_begin.record(stream)
         for i in range(steps):
-            st = stacks[i % n_sets]
-            for j in range(nl):
-                st.launch_one(j)
-                events[i * nl + j + 1].record(stream)
+            stacks[i % n_sets].forward()
+        e_end.record(stream)
         barrier()
     launches = lib.tracea_b200_launch_count() - launches_before   # counted by the library itself, this rank
     status = lib.tracea_b200_device_status(local_rank)
     if status != 0:
         raise RuntimeError("a conv kernel gave up a bounded wait (device status %d)" % status)
-    elapsed_ms = events[0].elapsed_time(events[-1])
+    elapsed_ms = e_begin.elapsed_time(e_end)
+    elapsed_max = shard.max_over_ranks(elapsed_ms)
+    ms_per_step = elapsed_max / steps
+    value = flops_step_rank * world * steps / (elapsed_max * 1e-3) / 1e12
+
+    # ---- the same K steps once more with an event after every launch: per-layer durations (each launch now starts
+    # only when the one before it has fully drained, so the three add up to slightly more than a step above)
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(steps * nl + 1)]
+    events[0].record(stream)
+    for i in range(steps):
+        st = stacks[i % n_sets]
+        for j in range(nl):
+            st.launch_one(j)
+            events[i * nl + j + 1].record(stream)
+    barrier()
     layer_ms = [0.0] * nl
     for i in range(steps):
         for j in range(nl):
             layer_ms[j] += events[i * nl + j].elapsed_time(events[i * nl + j + 1])
     layer_ms = [t / steps for t in layer_ms]
-    elapsed_max = shard.max_over_ranks(elapsed_ms)
-    ms_per_step = elapsed_max / steps
-    value = flops_step_rank * world * steps / (elapsed_max * 1e-3) / 1e12
 
     # ---- end to end through the C ABI with host tensors (H2D + D2H inside the timed region)
     e2e_steps = max(3, min(steps, 15))
@@ -293,6 +380,13 @@ def run_ours(args):
     e2e_mean = shard.max_over_ranks(sum(step_ms) / len(step_ms))
     e2e_value = flops_step_rank * world / (e2e_median * 1e-3) / 1e12
 
+    # ---- the same block as a fused graph from host memory: input H2D once, chain on device, output D2H once
+    e2e_graph = {}
+    try:
+        e2e_graph = time_e2e_graph(dev, n, stacks[0], specs, host["input"], flops_step_rank, world, e2e_steps, barrier, shard)
+    except Exception as e:
+        e2e_graph = {"error": "%s: %s" % (type(e).__name__, e)}
+
     # ---- the whole ResNet-50 conv stack (53 fused convs), images/s, as an extra figure
     extra = {}
     if not args.no_resnet:
@@ -336,9 +430,19 @@ def run_ours(args):
                      "tflops": r_flops * world / (r_ms * 1e-3) / 1e12,
                      "algorithmic_gbs_per_gpu": r_bytes / (r_ms * 1e-3) / 1e9, "launches_per_forward": len(rs),
                      "launch_mode": launch_mode}
+            extra["layers"] = stack_layer_table(net, rs, nb, load_peaks(), stream)
             del net, img, pooled
         except Exception as e:  # the extra figure must never take the headline line down
             extra = {"error": "%s: %s" % (type(e).__name__, e)}
+
+    # ---- the other benchmark configurations and the reference's own layer, rank 0's GPU only
+    configs = {}
+    if rank == 0 and not args.no_configs:
+        try:
+            configs = time_configs(dev, stream, lib, load_peaks())
+        except Exception as e:
+            configs = {"error": "%s: %s" % (type(e).__name__, e)}
+    barrier()
 
     # ---- the operators either side of the conv path (GEMM, ConvTranspose2d), rank 0's GPU only, extra figures
     next_ops = {}
@@ -366,33 +470,175 @@ def run_ours(args):
                        "l2": "%d rotating buffer sets of %.0f MB each (L2 is %.0f MB)" % (
                            n_sets, set_bytes / 1e6, L2_BYTES / 1e6)},
             "images_per_s": n * world / (ms_per_step * 1e-3),
+            "layers_note": "per-layer times come from a second pass of the same steps with a CUDA event after every "
+                           "launch; the headline pass has none, so that consecutive launches overlap (programmatic "
+                           "dependent launch)",
             "layers": [{"name": s.name, "ms": layer_ms[j], "tflops": resnet50.conv_flops(s, n) / layer_ms[j] / 1e9,
                         "algorithmic_gbs": resnet50.conv_bytes(s, n) / layer_ms[j] / 1e6}
                        for j, s in enumerate(specs)],
             "roofline": {"kernel": "conv2d_igemm_sm100_kernel<bf16,256,pair> on the 3x3 256->256 conv", "bound": "tensor",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                          "peak_source": "%s %s cuBLAS bf16" % (peaks["source"], "sustained" if sustained else "burst"),
-                         "traffic": CONV3X3_NCU_TRAFFIC_BYTES, "algorithmic_bytes": resnet50.conv_bytes(c2, n),
+                         "traffic": CONV3X3_NCU_TRAFFIC_BYTES, "traffic_source": CONV3X3_NCU_TRAFFIC_SOURCE,
+                         "algorithmic_bytes": resnet50.conv_bytes(c2, n),
                          "hbm_peak_gbs": peaks["hbm_gbs"]},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world,
                     "d2h_bytes_per_step": d2h * world, "steps": e2e_steps, "ms_per_step": e2e_median,
-                    "ms_per_step_mean": e2e_mean, "stat": "median of the per-step times"},
+                    "ms_per_step_mean": e2e_mean, "stat": "median of the per-step times",
+                    "what": "three tracea_conv2d calls on pinned host tensors: every tensor of every call crosses the bus",
+                    "bus_gbs_per_rank": (h2d + d2h) / (e2e_median * 1e-3) / 1e9},
+            "e2e_graph": e2e_graph,
             "gpu_launches": launches * world,
             "gpu_launches_per_step": launches / steps,
             "clocks": clocks.summary(),
+            "configs": configs,
             "resnet50": extra,
             "next_ops": next_ops,
         }
         if world == 1 and not args.no_cpu_baseline:
-            tf, ms, threads, done = time_cpu_baseline(8, 1000, 1, budget_s=12.0)
-            line["cpu_baseline"] = {
-                "value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                "sample": "bottleneck block on 8 of the 256 images, fp32, %d passes (%.0f ms each): im2col + packed "
-                          "AVX2/FMA GEMM restatement of the reference's CPU engine" % (done, ms)}
+            line["cpu_baseline"], line["cpu_baselines_other"] = cpu_baselines(8, budget_s=8.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def time_e2e_graph(dev, n, stack, specs, host_in, flops_step_rank, world, steps, barrier, shard):
+    """The bottleneck block as a GraphTopology (conv-bn-relu x2, conv-bn-add-relu), fused to three convs with the
+    BatchNorms folded, run from pinned HOST memory through GraphRunner.run_host: the timed region holds the copy of
+    the input to the device, the three kernels per image chunk and the copy of the output back."""
+    import torch
+    from tracea_b200 import graph as G
+    g = G.bottleneck_graph(n, 1024, 256, 14)
+    params = {}
+    for o in g["operators"]:
+        oid, name = G.op_id(o), G.op_body(o)["name"]
+        if G.op_kind(o) != "Input" or oid == 0:
+            continue
+        bn = int(name.split(".")[0])
+        c = 1024 if bn == 8 else 256
+        bias = stack.biases[specs[{2: 0, 5: 1, 8: 2}[bn]].name].cpu()
+        params[oid] = {"gamma": torch.ones(c), "beta": bias, "mean": torch.zeros(c), "var": torch.ones(c)}[name.split(".")[1]]
+    for conv_id, sp in zip((1, 4, 7), specs):
+        params[conv_id] = {"weight": stack.weights[sp.name].float().cpu()}
+    runner_ = G.GraphRunner(G.fuse(g), params, dtype=torch.bfloat16)
+    host_out = torch.empty((n, 1024, 14, 14), dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last).pin_memory()
+    runner_.run_host({0: host_in}, {7: host_out}, device=dev, chunks=8)
+    barrier()
+    ms = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        runner_.run_host({0: host_in}, {7: host_out}, device=dev, chunks=8)
+        ms.append((time.perf_counter() - t0) * 1e3)
+    barrier()
+    ms.sort()
+    med = shard.max_over_ranks(ms[len(ms) // 2])
+    h2d = host_in.numel() * host_in.element_size()
+    d2h = host_out.numel() * host_out.element_size()
+    return {"value": flops_step_rank * world / (med * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": med,
+            "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": steps,
+            "bus_gbs_per_rank": (h2d + d2h) / (med * 1e-3) / 1e9,
+            "what": "fused graph from pinned host memory (GraphRunner.run_host): input in, three convs per image chunk on "
+                    "the device, output out; copy-in, kernels and copy-out of different chunks overlap"}
+
+
+def stack_layer_table(net, rs, nb, peaks, stream):
+    """One row per distinct layer shape of the conv stack: launches, time (min of 3 eager passes, an event
+    between launches), roofline bound max(FLOPs / bf16 peak, algorithmic bytes / HBM bandwidth) and their ratio."""
+    import torch
+    from tracea_b200 import resnet50
+    reps = 3
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(rs) + 1)] for _ in range(reps)]
+    for r in range(reps):
+        ev[r][0].record(stream)
+        for j in range(len(rs)):
+            net.launch_one(j)
+            ev[r][j + 1].record(stream)
+    torch.cuda.synchronize()
+    rows = {}
+    for j, s in enumerate(rs):
+        ms = min(ev[r][j].elapsed_time(ev[r][j + 1]) for r in range(reps))
+        fl, by = resnet50.conv_flops(s, nb), resnet50.conv_bytes(s, nb)
+        bound = max(fl / (peaks["bf16_tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9)) * 1e3
+        key = "C%d H%d K%d %dx%d/%d %s" % (s.C, s.H, s.K, s.R, s.S, s.stride, s.epilogue)
+        row = rows.setdefault(key, {"shape": key, "count": 0, "ms": 0.0, "bound_ms": 0.0, "gflop": 0.0, "mbytes": 0.0})
+        row["count"] += 1
+        row["ms"] += ms
+        row["bound_ms"] += bound
+        row["gflop"] += fl / 1e9
+        row["mbytes"] += by / 1e6
+    out = []
+    for row in rows.values():
+        row["bound"] = "tensor" if row["gflop"] / peaks["bf16_tflops"] > row["mbytes"] / peaks["hbm_gbs"] else "hbm"
+        row["ratio_to_bound"] = row["ms"] / row["bound_ms"]
+        for k in ("ms", "bound_ms", "gflop", "mbytes", "ratio_to_bound"):
+            row[k] = round(row[k], 4)
+        out.append(row)
+    out.sort(key=lambda r: -(r["ms"] - r["bound_ms"]))
+    return out
+
+
+def time_configs(dev, stream, lib, peaks):
+    """The benchmark configurations that are not the headline block, each through tracea_conv2d on device tensors
+    laid out as the configuration states them (configuration 1 and 2: NCHW activations and OIHW weights, so the
+    layout adapters run inside every call and are part of the time), plus the reference's own benchmark layer
+    (3x3 64->64 at 56x56, examples/resnet_bench.rs:28-47) at its batch sizes. Device time: CUDA events around
+    `iters` back-to-back calls over rotating operand sets; host time: wall clock per call of issuing them."""
+    import torch
+    from tracea_b200 import ops
+    dt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+    def one(name, n, c, h, k, r, stride, pad, dtype, epilogue, nchw, iters, sets=3, peak_tf=None):
+        g = torch.Generator(device=dev).manual_seed(3)
+        cl = (lambda t: t.contiguous()) if nchw else (lambda t: t.contiguous(memory_format=torch.channels_last))
+        ho = (h + 2 * pad - r) // stride + 1
+        w = cl((torch.randn((k, c, r, r), device=dev, generator=g) * (2.0 / (c * r * r)) ** 0.5).to(dt[dtype]))
+        bias = torch.randn((k,), device=dev, generator=g) * 0.1 if "bias" in epilogue else None
+        kind = ops.parse_epilogue(epilogue or None, bias, None)
+        xs = [cl(torch.randn((n, c, h, h), device=dev, generator=g).to(dt[dtype])) for _ in range(sets)]
+        outs = [cl(torch.empty((n, k, ho, ho), device=dev, dtype=dt[dtype])) for _ in range(sets)]
+        call = lambda i: ops.conv2d_into(xs[i % sets], w, outs[i % sets], bias, None, stride, pad, 1, 1, kind)
+        for i in range(5):
+            call(i)
+        torch.cuda.synchronize(dev)
+        before = lib.tracea_b200_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for i in range(iters):
+            call(i)
+        e1.record(stream)
+        host_us = (time.perf_counter() - t0) / iters * 1e6
+        torch.cuda.synchronize(dev)
+        us = e0.elapsed_time(e1) / iters * 1e3
+        es = 4 if dtype == "f32" else 2
+        flops = 2.0 * n * ho * ho * k * c * r * r
+        nbytes = (n * c * h * h + k * c * r * r + n * k * ho * ho) * es + (k * 4 if bias is not None else 0)
+        peak = peak_tf if peak_tf is not None else peaks["bf16_tflops"]
+        bound_us = max(flops / (peak * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)) * 1e6
+        return {"workload": name, "us_per_call": us, "host_us_per_call": host_us, "tflops": flops / us / 1e6,
+                "algorithmic_gbs": nbytes / us / 1e3, "bound_us": bound_us, "frac_of_bound": bound_us / us,
+                "launches_per_call": (lib.tracea_b200_launch_count() - before) // iters,
+                "layout": "NCHW / OIHW as stated (adapters inside the call)" if nchw else "channels-last"}
+
+    tf32_peak = peaks["bf16_tflops"] / 2.0   # TF32 runs at half the bf16 rate
+    out = {
+        "config1": one("fp32 (TF32) x[1,64,56,56] * w[64,64,3,3] s1 p1 +bias+relu", 1, 64, 56, 64, 3, 1, 1, "f32",
+                       "bias+relu", True, 200, peak_tf=tf32_peak),
+        "config2": one("fp16 x[1,64,224,224] * w[128,64,3,3] s1 p0", 1, 64, 224, 128, 3, 1, 0, "f16", "", True, 100),
+        "config2_channels_last": one("fp16 x[1,64,224,224] * w[128,64,3,3] s1 p0, channels-last tensors", 1, 64, 224, 128, 3,
+                                     1, 0, "f16", "", False, 100),
+        "config4": one("bf16 x[256,128,56,56] * w[256,128,3,3] s2 p1 +bias+silu", 256, 128, 56, 256, 3, 2, 1, "bf16",
+                       "bias+silu", False, 30),
+    }
+    for batch in (32, 64, 256):
+        out["reference_layer_b%d" % batch] = one(
+            "bf16 x[%d,64,56,56] * w[64,64,3,3] s1 p1 +bias+relu (the reference's benchmark layer)" % batch, batch, 64, 56,
+            64, 3, 1, 1, "bf16", "bias+relu", False, 60 if batch < 256 else 30, sets=3 if batch < 256 else 3)
+    out["note"] = ("bound_us = max(FLOPs / measured tensor peak, algorithmic bytes / measured HBM bandwidth); TF32 is "
+                   "given half the bf16 peak; configurations 1 and 2 are single images: launch latency, not the roofline, "
+                   "sets their time")
+    return out
 
 
 def time_next_ops(dev, stream, lib, library_compare=False):
@@ -464,8 +710,7 @@ def main():
     ap.add_argument("--library-compare", action="store_true",
                     help="also time torch.matmul / torch conv_transpose2d (cuBLAS / cuDNN) on the same shapes, for context")
     ap.add_argument("--no-graph", action="store_true", help="launch the conv stack eagerly instead of from a CUDA graph")
-    ap.add_argument("--only-layer", choices=["c1", "c2", "c3"], default=None,
-                    help="profiling aid: only launch this layer of the block, print no JSON")
+    ap.add_argument("--no-configs", action="store_true", help="skip the figures of the other benchmark configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -1,5 +1,6 @@
-"""bench.py without a GPU: the reference arm (the CPU restatement of the reference's conv path) runs
-and prints one JSON line with the agreed keys; the default arm refuses to run without a CUDA device."""
+"""bench.py without a GPU: the reference arm (the reference's CPU conv path: the torch call its op makes on CPU
+tensors, with the SIMD-GEMM restatement beside it) runs and prints one JSON line with the agreed keys; the default
+arm refuses to run without a CUDA device."""
 import json
 import os
 import subprocess
@@ -17,7 +18,9 @@ def test_reference_arm_prints_one_json_line():
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["metric"] == "conv2d_tflops" and d["unit"] == "TFLOP/s"
     assert d["higher_is_better"] is True and d["value"] > 0 and d["steps"] == 2
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["kind"] == "reference" and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["value"] == d["value"]
+    assert d["cpu_baseline_simd_gemm_port"]["kind"] == "port" and d["cpu_baseline_simd_gemm_port"]["value"] > 0
     assert d["e2e"] == {"value": d["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert "workload" in d["config"]
 

@@ -54,29 +54,7 @@ def test_relu_with_two_consumers_of_the_conv_is_not_fused():
 
 
 def _bottleneck_graph(n=2, cin=64, width=16, h=8):
-    """conv1x1-bn-relu -> conv3x3-bn-relu -> conv1x1-bn -> add(input) -> relu, as unfused operators."""
-    ops, deps, oid = [G.input_op(0, "x")], [], [100]
-
-    def bn_params(c, bn_id):
-        ids = []
-        for name in ("gamma", "beta", "mean", "var"):
-            oid[0] += 1
-            ops.append(G.input_op(oid[0], "%d.%s" % (bn_id, name)))
-            ids.append(oid[0])
-            deps.append((oid[0], bn_id))
-        return ids
-
-    ops.append(G.conv2d(1, "c1", n, cin, h, h, width, 1, 1, 1, 0)); deps.append((0, 1))
-    ops.append(G.batchnorm(2, "bn1", n, width, h, h)); deps.append((1, 2)); bn_params(width, 2)
-    ops.append(G.relu(3, "r1", 0)); deps.append((2, 3))
-    ops.append(G.conv2d(4, "c2", n, width, h, h, width, 3, 3, 1, 1)); deps.append((3, 4))
-    ops.append(G.batchnorm(5, "bn2", n, width, h, h)); deps.append((4, 5)); bn_params(width, 5)
-    ops.append(G.relu(6, "r2", 0)); deps.append((5, 6))
-    ops.append(G.conv2d(7, "c3", n, width, h, h, cin, 1, 1, 1, 0)); deps.append((6, 7))
-    ops.append(G.batchnorm(8, "bn3", n, cin, h, h)); deps.append((7, 8)); bn_params(cin, 8)
-    ops.append(G.add(9, "add", 0)); deps.append((8, 9)); deps.append((0, 9))
-    ops.append(G.relu(10, "r3", 0)); deps.append((9, 10))
-    return {"operators": ops, "dependencies": deps}
+    return G.bottleneck_graph(n, cin, width, h)
 
 
 def test_bottleneck_block_fuses_to_three_convs():
@@ -157,3 +135,10 @@ def test_fused_bottleneck_graph_runs_on_the_gpu_and_matches_torch():
     torch.cuda.synchronize()
     err = (out.float().cpu() - want).abs().max() / want.abs().max()
     assert err <= 1.5e-2        # three chained TF32 convs, 5e-3 each
+    # the same graph from host memory: input copied in once, only the last conv's output copied back, in image chunks
+    host_in = x.contiguous(memory_format=torch.channels_last).pin_memory()
+    host_out = torch.empty((n, cin, h, h)).contiguous(memory_format=torch.channels_last).pin_memory()
+    for chunks in (1, 3):
+        host_out.fill_(float("nan"))
+        runner.run_host({0: host_in}, {7: host_out}, chunks=chunks)
+        assert torch.equal(host_out, out.cpu()), chunks

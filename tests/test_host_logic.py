@@ -88,3 +88,21 @@ def test_stage3_block_numbers():
     assert abs(resnet50.conv_flops(c2, 256) / 1e9 - 59.19) < 0.01
     assert abs(resnet50.conv_bytes(c2, 256) / 1e6 - 52.6) < 0.1
     assert abs(resnet50.conv_bytes(c3, 256) / 1e6 - 231.7) < 0.1
+
+
+def test_layer_bench_example_parses_its_arguments():
+    """examples/layer_bench.py: presets expand to the reference's benchmark layers, dimension counts are checked."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "layer_bench.py")
+    spec = importlib.util.spec_from_file_location("layer_bench", path)
+    lb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(lb)
+    op, dims, args = lb.parse(["preset", "resnet50-3x3-64"])
+    assert (op, dims) == ("conv", [64, 64, 56, 64, 3, 1, 1]) and args.epilogue == "bias+relu"
+    op, dims, args = lb.parse(["conv", "256", "64", "56", "64", "3", "1", "1", "--dtype", "f16", "--launch-only"])
+    assert dims == [256, 64, 56, 64, 3, 1, 1] and args.dtype == "f16" and args.launch_only
+    assert lb.parse(["gemm", "8192", "8192", "8192"])[1] == [8192, 8192, 8192]
+    for bad in (["gemm", "1", "2"], ["preset", "nope"], ["conv", "1", "2", "3"]):
+        with pytest.raises(SystemExit):
+            lb.parse(bad)

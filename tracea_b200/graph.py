@@ -149,6 +149,33 @@ def fuse(graph):
     return {"operators": ops, "dependencies": deps}
 
 
+# --------------------------------------------------------------------------------- a ready-made graph
+def bottleneck_graph(n, cin, width, h):
+    """A ResNet bottleneck block as UNFUSED operators: conv1x1-bn-relu -> conv3x3-bn-relu -> conv1x1-bn -> add(input)
+    -> relu (the block shape of src/bin/network_bench.rs:41-247). Op ids: 0 input, 1 / 4 / 7 the convs, 2 / 5 / 8 their
+    BatchNorms, 9 the add, 10 the last ReLU; the BatchNorm parameter inputs are numbered from 101 in the order
+    gamma, beta, mean, var per BatchNorm. `fuse` turns it into three convs."""
+    ops, deps, oid = [input_op(0, "x")], [], [100]
+
+    def bn_params(bn_id):
+        for name in ("gamma", "beta", "mean", "var"):
+            oid[0] += 1
+            ops.append(input_op(oid[0], "%d.%s" % (bn_id, name)))
+            deps.append((oid[0], bn_id))
+
+    ops.append(conv2d(1, "c1", n, cin, h, h, width, 1, 1, 1, 0)); deps.append((0, 1))
+    ops.append(batchnorm(2, "bn1", n, width, h, h)); deps.append((1, 2)); bn_params(2)
+    ops.append(relu(3, "r1", 0)); deps.append((2, 3))
+    ops.append(conv2d(4, "c2", n, width, h, h, width, 3, 3, 1, 1)); deps.append((3, 4))
+    ops.append(batchnorm(5, "bn2", n, width, h, h)); deps.append((4, 5)); bn_params(5)
+    ops.append(relu(6, "r2", 0)); deps.append((5, 6))
+    ops.append(conv2d(7, "c3", n, width, h, h, cin, 1, 1, 1, 0)); deps.append((6, 7))
+    ops.append(batchnorm(8, "bn3", n, cin, h, h)); deps.append((7, 8)); bn_params(8)
+    ops.append(add(9, "add", 0)); deps.append((8, 9)); deps.append((0, 9))
+    ops.append(relu(10, "r3", 0)); deps.append((9, 10))
+    return {"operators": ops, "dependencies": deps}
+
+
 # --------------------------------------------------------------------------------- BatchNorm folding
 def fold_batchnorm(weight, gamma, beta, mean, var, eps, conv_bias=None):
     """(x*w [+ b] - mean) * rsqrt(var + eps) * gamma + beta  ==  x*(w*scale) + shift, per output channel:
@@ -266,3 +293,55 @@ class GraphRunner:
             values[oid] = ops.conv2d_nchw(x, dev_w, dev_bias, res, stride, padding, 1, 1,
                                           None if epi == "identity" else epi, channels_last_out=True)
         return values
+
+    def run_host(self, inputs, outputs, device=None, chunks=8):
+        """The same graph for tensors that live in HOST memory: `inputs` {input op id: CPU tensor} are copied to
+        the device once, the whole chain of convs runs there, and only the tensors named in `outputs`
+        {conv op id: CPU tensor to fill} come back -- intermediates never cross the bus (the reference's executor
+        keeps them in its device arena, src/runtime/manager/graph.rs:7-50, src/runtime/executor/mod.rs:79-85).
+        A convolution never mixes images, so the batch is cut into `chunks` slices whose copy-in, kernels and
+        copy-out overlap on three streams (the bus is full duplex). Pinned host tensors make the copies
+        asynchronous; pageable ones work, without the overlap. Returns when `outputs` are filled."""
+        import torch
+        from . import ops
+        dev = torch.device(device if device is not None else "cuda")
+        n = next(iter(inputs.values())).shape[0]
+        if any(t.shape[0] != n for t in inputs.values()):
+            raise ValueError("every input must have the same batch size")
+        chunks = max(1, min(chunks, n))
+        cl = torch.channels_last
+        key = (dev, tuple(sorted((i, tuple(t.shape), t.dtype) for i, t in inputs.items())), tuple(sorted(outputs)))
+        st = self._host_state.get(key) if hasattr(self, "_host_state") else None
+        if st is None:
+            if not hasattr(self, "_host_state"):
+                self._host_state = {}
+            st = {
+                "in": {i: torch.empty(t.shape, dtype=t.dtype, device=dev).contiguous(memory_format=cl)
+                       for i, t in inputs.items()},
+                "copy_in": torch.cuda.Stream(dev), "copy_out": torch.cuda.Stream(dev),
+                "ev_in": [], "ev_done": [],
+            }
+            self._host_state[key] = st
+        while len(st["ev_in"]) < chunks:
+            st["ev_in"].append(torch.cuda.Event())
+            st["ev_done"].append(torch.cuda.Event())
+        main = torch.cuda.current_stream(dev)
+        st["copy_in"].wait_stream(main)
+        st["copy_out"].wait_stream(main)
+        bounds = [(n * c // chunks, n * (c + 1) // chunks) for c in range(chunks)]
+        for c, (a, b) in enumerate(bounds):
+            with torch.cuda.stream(st["copy_in"]):
+                for i, t in inputs.items():
+                    st["in"][i][a:b].copy_(t[a:b], non_blocking=True)
+                st["ev_in"][c].record(st["copy_in"])
+            main.wait_event(st["ev_in"][c])
+            values = self.run({i: st["in"][i][a:b] for i in inputs})
+            st["ev_done"][c].record(main)
+            with torch.cuda.stream(st["copy_out"]):
+                st["copy_out"].wait_event(st["ev_done"][c])
+                for oid, host in outputs.items():
+                    values[oid].record_stream(st["copy_out"])
+                    host[a:b].copy_(values[oid], non_blocking=True)
+        main.wait_stream(st["copy_out"])
+        main.synchronize()
+        return outputs
