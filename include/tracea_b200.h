@@ -254,6 +254,14 @@ void tracea_shutdown(void);
  * has no counterpart: its kernels spin without limit. */
 uint32_t tracea_b200_device_status(int32_t device_id);
 
+/* For tests of the failure path only. Every wait inside the kernels is bounded; a wait that runs out makes its role
+ * record a code, the CTA unwind and the kernel return normally. wait_limit_cycles > 0 replaces the limit of a single
+ * wait (default about two seconds) for the launches that follow; producer_stop_after >= 0 makes the TMA producer of
+ * every CTA of those launches stop after that many pipeline stages and leave normally, so that the waits downstream
+ * of it run out -- nothing faults, traps or spins without limit. (0, -1) restores normal operation. Process-wide.
+ * No counterpart in the reference (its kernels wait without limit, src/backend/cuda/primitives.rs:70-121). */
+void tracea_b200_test_hooks(int64_t wait_limit_cycles, int32_t producer_stop_after);
+
 /* Byte counters of the library's stream-ordered scratch pool on `device_id`:
  * stats = {reserved now, reserved high-water mark, in use now, in-use high-water mark}; reset_high != 0 resets
  * the two high-water marks after reading. Returns 1, 0 when the device has no pool yet (stats all zero), -1 on

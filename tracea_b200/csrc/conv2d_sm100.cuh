@@ -39,7 +39,7 @@ constexpr int kBlockM = 128;          // output pixels per tile = TMEM lanes
 constexpr int kStageKBytes = 128;     // bytes of K per smem row per pipeline stage
 constexpr int kNumThreads = 320;      // warp 0 TMA, warp 1 MMA, warps 2..5 and 6..9 two epilogue groups
 constexpr int kMaxStages = 12;
-constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 1.9 GHz, per wait
+constexpr long long kWaitLimitCycles = 4000000000LL;  // default limit of one wait: ~2 s at 1.9 GHz (ConvKernelArgs::wait_limit)
 
 // Device-side error codes written to ConvKernelArgs::status (0 = fine).
 enum : uint32_t {
@@ -109,6 +109,9 @@ struct ConvKernelArgs {
   int res_tma;            // 1: residual is dense row-major too and is TMA-loaded into the staging boxes
   // error reporting: 4 words {code, block, detail, 0}; first error wins
   uint32_t* status;
+  long long wait_limit;   // cycles any single wait may take before the role gives up (args.wait_limit unless a test shortens it)
+  int test_producer_stop; // test hook, -1 in normal use: the TMA producer stops issuing after this many stages and
+                          // leaves normally, so that the waits downstream of it run out
   long long* prof;        // cycle counters, only written by -DTB200_PROFILE builds
 };
 
@@ -504,13 +507,14 @@ __device__ __noinline__ void sk_dump_partial(uint32_t taddr0, int chunks, float4
 
 // Lane 0 waits until `expected` other pieces have counted themselves done on cnt[1], then zeroes the tile's two
 // counters (every party has passed both by then). False when the wait gave up.
-__device__ __noinline__ bool sk_wait_partials(uint32_t* cnt, uint32_t expected, volatile uint32_t* abort_flag, int lane) {
+__device__ __noinline__ bool sk_wait_partials(uint32_t* cnt, uint32_t expected, volatile uint32_t* abort_flag,
+                                              long long limit_cycles, int lane) {
   bool all_in = true;
   if (lane == 0) {
     const long long t_start = clock64();
     uint32_t spins = 0;
     while (ptx::ld_acquire_gpu(cnt + 1) != expected) {
-      if ((++spins & 0xffu) == 0 && (*abort_flag != 0u || clock64() - t_start > kWaitLimitCycles)) {
+      if ((++spins & 0xffu) == 0 && (*abort_flag != 0u || clock64() - t_start > limit_cycles)) {
         all_in = false;
         break;
       }
@@ -741,7 +745,8 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       WorkIter witer;
       witer.template init<kSplit>(args, worker, k_iters);
       WorkItem item;
-      while (ok && witer.template next<kSplit>(item, args, num_workers, k_iters)) {
+      bool stopped = false;
+      while (ok && !stopped && witer.template next<kSplit>(item, args, num_workers, k_iters)) {
         tile_coords(item.tile, m_tile, n_tile);
         const int m0 = args.m_begin + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;   // this CTA's 128 pixels
         const int q0 = m0 % args.Wo;
@@ -775,8 +780,12 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
             k_coord += item.k_begin * args.chunk_elems + tap * args.b_jump_s + tap_r * args.b_jump_r;
           }
           for (int it = item.k_begin; it < item.k_end; ++it) {
+            if (issued == args.test_producer_stop) {   // test hook: go silent, leave normally
+              stopped = true;
+              break;
+            }
             TB200_PROF_T(tw);
-            if (!slot_free && !mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) {
+            if (!slot_free && !mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, args.wait_limit)) {
               report_error(args, abort_p, kErrProducerWait, (uint32_t)it);
               ok = false;
               break;
@@ -818,7 +827,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           // narrow k-chunks (several per stage): whole tiles only, the host never splits these over K
           int chunk = 0, tap_r = 0, tap_s = 0, cc = 0;
           for (int it = 0; it < k_iters; ++it) {
-            if (!mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) {
+            if (!mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, args.wait_limit)) {
               report_error(args, abort_p, kErrProducerWait, (uint32_t)it);
               ok = false;
               break;
@@ -861,7 +870,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (ok) {
         const int pending = issued < num_stages ? issued : num_stages;
         for (int i = 0; i < pending; ++i) {
-          if (!mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, kWaitLimitCycles)) break;
+          if (!mbar_wait_bounded(empty_addr, phase ^ 1u, abort_p, args.wait_limit)) break;
           stage_addr += kStageBytes; empty_addr += 8u;
           if (stage_addr == ring_end) { stage_addr = smem_base; empty_addr = empty_bar0; phase ^= 1u; }
         }
@@ -904,7 +913,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int buf = local_tile & 1;
         const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
         TB200_PROF_T(tw0);
-        if (!mbar_wait_bounded(tempty_bar(buf), (use & 1u) ^ 1u, abort_p, kWaitLimitCycles)) {
+        if (!mbar_wait_bounded(tempty_bar(buf), (use & 1u) ^ 1u, abort_p, args.wait_limit)) {
           report_error(args, abort_p, kErrMmaWaitTmem, (uint32_t)local_tile);
           ok = false;
           break;
@@ -915,7 +924,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         for (int it = item.k_begin; it < item.k_end; ++it) {
           const bool first = it == item.k_begin;   // the piece's first MMA overwrites the accumulator
           TB200_PROF_T(tw1);
-          if (!stage_ready && !mbar_wait_bounded(full_addr, phase, abort_p, kWaitLimitCycles)) {
+          if (!stage_ready && !mbar_wait_bounded(full_addr, phase, abort_p, args.wait_limit)) {
             report_error(args, abort_p, kErrMmaWaitFull, (uint32_t)it);
             ok = false;
             break;
@@ -1075,7 +1084,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (pi.k_end - pi.k_begin == k_iters) break;          // whole tiles from here on
         if (!kRows2 && (l & 1) != egroup) continue;           // the other group's item
         const int buf = kRows2 ? (l & 1) : egroup;
-        const bool ready = mbar_wait_bounded(tfull_bar(buf), 0u, abort_p, kWaitLimitCycles);   // first use of the buffer
+        const bool ready = mbar_wait_bounded(tfull_bar(buf), 0u, abort_p, 2 * args.wait_limit);   // first use of the buffer
         if (!__all_sync(0xffffffffu, ready)) {
           if (lane == 0) report_error(args, abort_p, kErrEpilogueWait, (uint32_t)l);
           ok = false;
@@ -1108,7 +1117,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           continue;
         }
         TB200_PROF_T(tsw);
-        if (!sk_wait_partials(cnt, static_cast<uint32_t>(sk_pieces - 1), abort_p, lane)) {
+        if (!sk_wait_partials(cnt, static_cast<uint32_t>(sk_pieces - 1), abort_p, args.wait_limit, lane)) {
           if (lane == 0) report_error(args, abort_p, kErrSplitWait, (uint32_t)l);
           ok = false;
           break;
@@ -1173,7 +1182,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (!partial) request_first_residual();
 
       TB200_PROF_T(tw2);
-      const bool ready = mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_p, kWaitLimitCycles);
+      const bool ready = mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_p, 2 * args.wait_limit);
       TB200_PROF_ADD(prof_wacc, tw2);
       if (!__all_sync(0xffffffffu, ready)) {      // keep the warp converged for tcgen05.ld
         if (lane == 0) report_error(args, abort_p, kErrEpilogueWait, (uint32_t)local_tile);
@@ -1214,7 +1223,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (res_tma) {
           TB200_PROF_T(tw3);
           const bool landed = mbar_wait_bounded(res_bar(ew, box), (box_phase >> box) & 1u, abort_p,
-                                                kWaitLimitCycles);
+                                                args.wait_limit);
           TB200_PROF_ADD(prof_wres, tw3);
           if (!__all_sync(0xffffffffu, landed)) {
             if (lane == 0) report_error(args, abort_p, kErrResidualWait, (uint32_t)local_tile);

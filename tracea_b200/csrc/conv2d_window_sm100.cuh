@@ -54,6 +54,8 @@ struct WindowKernelArgs {
   int bias_is_f32;
   int act;
   uint32_t* status;
+  long long wait_limit;   // cycles any single wait may take before the role gives up
+  int test_producer_stop; // test hook, -1 in normal use: the TMA producer stops after this many windows
   long long* prof;        // cycle counters, only written by -DTB200_PROFILE builds
 };
 
@@ -253,8 +255,9 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
       uint32_t it = 0;
       bool ok = true;
       for (int j = pair; j < args.pair_tiles && ok; j += num_pairs, ++it) {
+        if (static_cast<int>(it) == args.test_producer_stop) break;   // test hook: go silent, leave normally
         const uint32_t slot = it & 1u, use = it >> 1;
-        if (!mbar_wait_bounded(win_empty(slot), (use & 1u) ^ 1u, abort_p, kWaitLimitCycles)) {
+        if (!mbar_wait_bounded(win_empty(slot), (use & 1u) ^ 1u, abort_p, args.wait_limit)) {
           report_error_status(args.status, abort_p, kErrProducerWait, it);
           ok = false;
           break;
@@ -269,7 +272,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
         const uint32_t pending = it < 2u ? it : 2u;
         for (uint32_t i = 0; i < pending; ++i) {
           const uint32_t q = it - pending + i;
-          if (!mbar_wait_bounded(win_empty(q & 1u), (q >> 1) & 1u, abort_p, kWaitLimitCycles)) break;
+          if (!mbar_wait_bounded(win_empty(q & 1u), (q >> 1) & 1u, abort_p, args.wait_limit)) break;
         }
       } else {
         const long long t0 = clock64();
@@ -280,7 +283,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
     // ------------------------------------------------------------ MMA issuer (one thread of the leader CTA)
     if (lane == 0 && leader) {
       const uint32_t desc_hi = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);   // SBO 1024 B, SWIZZLE_128B
-      bool ok = mbar_wait_bounded(w_bar, 0u, abort_p, kWaitLimitCycles);
+      bool ok = mbar_wait_bounded(w_bar, 0u, abort_p, args.wait_limit);
       if (!ok) report_error_status(args.status, abort_p, kErrMmaWaitFull, 0xffffu);
       uint32_t it = 0;
       long long prof_wfull = 0, prof_wtmem = 0;
@@ -290,14 +293,14 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
         const uint32_t slot = it & 1u, use = it >> 1;   // window slot and accumulator buffer alternate together
         const int nblk = j < args.pair_tiles_full ? args.nblk_full : args.nblk_short;
         TB200_PROF_T(tw0);
-        if (!mbar_wait_bounded(tempty_bar(slot), (use & 1u) ^ 1u, abort_p, kWaitLimitCycles)) {
+        if (!mbar_wait_bounded(tempty_bar(slot), (use & 1u) ^ 1u, abort_p, args.wait_limit)) {
           report_error_status(args.status, abort_p, kErrMmaWaitTmem, it);
           ok = false;
           break;
         }
         TB200_PROF_ADD(prof_wtmem, tw0);
         TB200_PROF_T(tw1);
-        if (!mbar_wait_bounded(win_full(slot), use & 1u, abort_p, kWaitLimitCycles)) {
+        if (!mbar_wait_bounded(win_full(slot), use & 1u, abort_p, args.wait_limit)) {
           report_error_status(args.status, abort_p, kErrMmaWaitFull, it);
           ok = false;
           break;
@@ -361,7 +364,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
       const uint32_t buf = it & 1u, use = it >> 1;
       const Tile t = tile_of(j);
       TB200_PROF_T(tw2);
-      const bool ready = mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_p, kWaitLimitCycles);
+      const bool ready = mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_p, 2 * args.wait_limit);
       TB200_PROF_ADD(prof_wacc, tw2);
       if (!__all_sync(0xffffffffu, ready)) {
         if (lane == 0) report_error_status(args.status, abort_p, kErrEpilogueWait, it);

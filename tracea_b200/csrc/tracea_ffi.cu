@@ -99,6 +99,10 @@ constexpr int kMaxDevices = 64;
 std::mutex g_dev_mu[kMaxDevices];
 std::mutex g_driver_mu;
 DeviceState g_dev[kMaxDevices];
+// Test hooks (tracea_b200_test_hooks): a shortened wait limit and a producer that goes silent, so that a test can
+// make a bounded wait run out without hanging anything. Off (0 / -1) unless a test sets them.
+std::atomic<long long> g_test_wait_limit{0};
+std::atomic<int> g_test_producer_stop{-1};
 // "opt-in shared memory size has been set for this kernel variant on this device":
 // [device][dtype][bn index][tiling: single CTA / CTA pair / two row blocks; x3: plain, coop epilogue, K-split].
 // Setting the attribute twice is harmless, so a relaxed flag is enough.
@@ -727,6 +731,11 @@ bool try_resident_filter_conv(DeviceState& st, const View4& x, const void* w_ptr
   }
   a.act = epi.act;
   a.status = st.status;
+  {
+    const long long lim = g_test_wait_limit.load(std::memory_order_relaxed);
+    a.wait_limit = lim > 0 ? lim : tb200::kWaitLimitCycles;
+    a.test_producer_stop = g_test_producer_stop.load(std::memory_order_relaxed);
+  }
 #ifdef TB200_PROFILE
   {
     const char* pp = getenv("TRACEA_B200_PROF_PTR");
@@ -1090,6 +1099,11 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
   }
   a.act = epi.act;
   a.status = st.status;
+  {
+    const long long lim = g_test_wait_limit.load(std::memory_order_relaxed);
+    a.wait_limit = lim > 0 ? lim : tb200::kWaitLimitCycles;
+    a.test_producer_stop = g_test_producer_stop.load(std::memory_order_relaxed);
+  }
   // channel-contiguous output (and residual, if any) that the TMA unit cannot address as one matrix: the kernel
   // variant whose epilogue writes its staging boxes out itself, whole 128-byte rows at a time
   const bool coop = !a.out_tma && a.out_vec && (a.residual == nullptr || a.res_vec);
@@ -1942,6 +1956,11 @@ int32_t tracea_b200_conv_transpose_plan(uint32_t in_extent, uint32_t out_extent,
     if (ax.T > 0 && ax.empty) o[2] = -1;   // no tap reaches this phase: its single tap is a zero
   }
   return static_cast<int32_t>(stride);
+}
+
+void tracea_b200_test_hooks(int64_t wait_limit_cycles, int32_t producer_stop_after) {
+  g_test_wait_limit.store(wait_limit_cycles > 0 ? wait_limit_cycles : 0, std::memory_order_relaxed);
+  g_test_producer_stop.store(producer_stop_after >= 0 ? producer_stop_after : -1, std::memory_order_relaxed);
 }
 
 uint64_t tracea_b200_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }

@@ -24,7 +24,7 @@ DTYPE_FLOAT32, DTYPE_FLOAT16, DTYPE_BFLOAT16, DTYPE_INT32, DTYPE_INT8 = 0, 1, 2,
 EXPORTED_SYMBOLS = (
     "tracea_conv2d", "tracea_conv2d_v0", "tracea_conv2d_noalloc", "tracea_get_last_error", "tracea_clear_error",
     "tracea_version_major", "tracea_version_minor", "tracea_version_patch", "tracea_init",
-    "tracea_shutdown", "tracea_b200_device_status", "tracea_b200_launch_count", "tracea_b200_launch_count_of", "tracea_b200_pool_stats",
+    "tracea_shutdown", "tracea_b200_device_status", "tracea_b200_launch_count", "tracea_b200_launch_count_of", "tracea_b200_test_hooks", "tracea_b200_pool_stats",
     "tracea_b200_conv_transpose_plan",
     "tracea_gemm", "tracea_conv_transpose2d", "tracea_conv2d_prepack_bytes", "tracea_conv2d_prepack",
     "tracea_gemm_prepack_b_bytes", "tracea_gemm_prepack_b",
@@ -124,6 +124,8 @@ def load():
     lib.tracea_b200_device_status.restype = ctypes.c_uint32
     lib.tracea_b200_pool_stats.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_uint64), ctypes.c_int32]
     lib.tracea_b200_pool_stats.restype = ctypes.c_int32
+    lib.tracea_b200_test_hooks.argtypes = [ctypes.c_int64, ctypes.c_int32]
+    lib.tracea_b200_test_hooks.restype = None
     lib.tracea_b200_launch_count_of.argtypes = [ctypes.c_int32]
     lib.tracea_b200_launch_count_of.restype = ctypes.c_uint64
     lib.tracea_b200_launch_count.argtypes = []
