@@ -258,13 +258,17 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    # stdout carries exactly one JSON line: whatever libraries write to file descriptor 1 meanwhile (NCCL's version
+    # banner and, when NCCL_DEBUG asks for them, its log lines) is sent to stderr, where it stays readable
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the library has no CPU compute path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's own log lines, if asked for, stay off stdout
         dist.init_process_group("nccl", device_id=dev)
     if rank == 0:
         build.build()
@@ -497,6 +501,8 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], line["cpu_baselines_other"] = cpu_baselines(8, budget_s=8.0)
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
