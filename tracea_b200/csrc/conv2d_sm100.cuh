@@ -1026,13 +1026,23 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // This group's items: every second item of the worker (group e drains TMEM accumulator e) -- or, with
     // two-row-block tiles, every item, of which the group takes the 128-row block `egroup`. The iterator runs one
     // item ahead so that the next tile's bias can be fetched early.
+    // The worker's LAST item is shared by both groups: nothing overlaps its epilogue any more (the next kernel
+    // cannot start before this one ends), so the group that would idle takes every second 128-byte column group of
+    // it -- the same TMEM lanes belong to warp w and warp w + 4 -- and the exposed tail of the launch is halved.
+    int last_item = -1;
+    if constexpr (!kRows2 && kGroups >= 2) {
+      WorkIter cnt;
+      cnt.template init<kSplit>(args, worker, k_iters);
+      WorkItem t;
+      while (cnt.template next<kSplit>(t, args, num_workers, k_iters)) ++last_item;
+    }
     WorkIter witer;
     witer.template init<kSplit>(args, worker, k_iters);
     int local_next = 0;                            // local index of the item witer.next() yields next
     auto next_mine = [&](WorkItem& it, int& local) -> bool {
       while (witer.template next<kSplit>(it, args, num_workers, k_iters)) {
         const int l = local_next++;
-        if (kRows2 || (l & 1) == egroup) {
+        if (kRows2 || (l & 1) == egroup || l == last_item) {
           local = l;
           return true;
         }
@@ -1049,7 +1059,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       WorkItem ni;
       while (pk.template next<kSplit>(ni, args, num_workers, k_iters)) {
         const int l = pl++;
-        if (kRows2 || (l & 1) == egroup) {
+        if (kRows2 || (l & 1) == egroup || l == last_item) {
           int mm, nn;
           tile_coords(ni.tile, mm, nn);
           if (nn != cur_n) fetch_bias(nn);
@@ -1133,7 +1143,12 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     while (ok && next_mine(item, local_tile)) {
       const int tile = item.tile;
       tile_coords(tile, m_tile, n_tile);
-      const int buf = kRows2 ? (local_tile & 1) : egroup;
+      const int buf = local_tile & 1;              // = egroup for the group's own items
+      const bool partial = kSplit && item.k_end - item.k_begin != k_iters;   // one piece of a tile split over K
+      // column groups this warp takes: all of them, or -- on the shared last item -- every second one
+      const bool shared = !kRows2 && local_tile == last_item && !partial;
+      const int g_first = shared && (local_tile & 1) != egroup ? 1 : 0;
+      const int g_step = shared ? 2 : 1;
       const uint32_t use = static_cast<uint32_t>(local_tile >> 1);
       const int n_base = n_tile * BN;
       const int row_block = kPair ? static_cast<int>(cta_rank) : (kRows2 ? egroup : 0);   // which 128 rows of the tile
@@ -1166,18 +1181,18 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // Residual box of the tile's first live group: requested before the accumulator is waited for.
       // Box `box` was last stored from two groups ago; only the newer store may still be pending.
       auto request_first_residual = [&]() {
-        if (res_tma && n_base < args.K_out) {
+        if (res_tma && n_base + g_first * kGroupCols < args.K_out) {
           if (lane == 0) {
             bulk_wait_group_read<1>();
             mbar_arrive_expect_tx(res_bar(ew, box), kStagingBoxBytes);
-            tma_load_2d(stg0 + box * kStagingBoxBytes, &tmap_res, res_bar(ew, box), n_base, m_row0);
+            tma_load_2d(stg0 + box * kStagingBoxBytes, &tmap_res, res_bar(ew, box), n_base + g_first * kGroupCols, m_row0);
           }
         }
       };
-      const bool partial = kSplit && item.k_end - item.k_begin != k_iters;   // one piece of a tile split over K
       if constexpr (kSplit) {
-        // a piece whose partial sums went to another CTA is finished; one that collected the others' is a whole tile now
-        if (partial && ((sk_reduced >> local_tile) & 1u) == 0u) continue;
+        // a piece whose partial sums went to another CTA is finished; one that collected the others' is a whole tile
+        // now (for the group that collected them: a piece is never shared between the groups)
+        if (partial && (((sk_reduced >> local_tile) & 1u) == 0u || (local_tile & 1) != egroup)) continue;
       }
       if (!partial) request_first_residual();
 
@@ -1199,7 +1214,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
 
 #pragma unroll 1
-      for (int g = 0; g < kGroups; ++g) {
+      for (int g = g_first; g < kGroups; g += g_step) {
         const int n0 = n_base + g * kGroupCols;
         const bool group_live = n0 < args.K_out;   // warp-uniform: false when the group is past K_out
         const uint32_t stg = stg0 + box * kStagingBoxBytes;
@@ -1209,8 +1224,9 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         for (int h = 0; h < kLdPerGroup; ++h) tmem_ld_32x32(taddr0 + g * kGroupCols + h * 32, v[h]);
         tmem_ld_wait();
         TB200_PROF_ADD(prof_ld, tl);
-        if (g == kGroups - 1) {
-          // the accumulator is in registers now: hand the TMEM buffer back to the MMA issuer
+        if (g == kGroups - 1 && !shared) {
+          // the accumulator is in registers now: hand the TMEM buffer back to the MMA issuer (nobody waits for
+          // the buffer of the worker's last item, which two groups drain)
           tc_fence_before();
           __syncwarp();
           if (lane == 0) {
@@ -1233,12 +1249,12 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           box_phase ^= (1u << box);
           // Now that this group's residual has landed, fetch the NEXT group's into the other box. That
           // box was stored from one group ago; its store has had this group's wait to be read out.
-          if (g + 1 < kGroups && n0 + kGroupCols < args.K_out) {
+          if (g + g_step < kGroups && n0 + g_step * kGroupCols < args.K_out) {
             if (lane == 0) {
               const uint32_t nb = box ^ 1u;
               bulk_wait_group_read<0>();
               mbar_arrive_expect_tx(res_bar(ew, nb), kStagingBoxBytes);
-              tma_load_2d(stg0 + nb * kStagingBoxBytes, &tmap_res, res_bar(ew, nb), n0 + kGroupCols, m_row0);
+              tma_load_2d(stg0 + nb * kStagingBoxBytes, &tmap_res, res_bar(ew, nb), n0 + g_step * kGroupCols, m_row0);
             }
           }
         } else if (args.out_tma) {
