@@ -397,9 +397,8 @@ def run_ours(args):
         try:
             nb = max(1, args.resnet_batch // world)   # config 5 shards a fixed global batch (strong scaling)
             rs = resnet50.resnet50_convs()
-            img = torch.zeros((nb, 8, 224, 224), device=dev, dtype=torch.bfloat16).contiguous(
-                memory_format=torch.channels_last)
-            img[:, :3] = torch.randn((nb, 3, 224, 224), device=dev).to(torch.bfloat16)
+            img = torch.randn((nb, 3, 224, 224), device=dev).to(torch.bfloat16).contiguous(
+                memory_format=torch.channels_last)      # a true 3-channel NHWC image
             pooled = torch.randn((nb, 64, 56, 56), device=dev).abs_().to(torch.bfloat16).contiguous(
                 memory_format=torch.channels_last)
             net = runner.ConvStack(rs, nb, "bf16", dev, seed=11, inputs={"image": img, "pooled": pooled})

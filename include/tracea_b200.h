@@ -274,7 +274,8 @@ int32_t tracea_b200_pool_stats(int32_t device_id, uint64_t stats[4], int32_t res
 uint64_t tracea_b200_launch_count(void);
 
 /* The same count for one kind of kernel: 0 the general implicit-GEMM conv kernel, 1 its instantiations that cut tiles
- * over K, 2 the resident-filter kernel (stride-1 small filters over 64-channel activations), 3 layout adapters.
+ * over K, 2 the resident-filter kernel (stride-1 small filters over 64-channel activations), 3 layout adapters,
+ * 4 the row-band kernel (few-channel 16-bit images such as the RGB stem).
  * Lets tests and benchmarks see which path a call took. 0 for any other `kind`. No counterpart in the reference. */
 uint64_t tracea_b200_launch_count_of(int32_t kind);
 

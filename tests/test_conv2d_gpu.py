@@ -185,8 +185,7 @@ def test_config4_strided_downsample_bias_silu():
 
 
 def _stack_inputs(n):
-    img = np.zeros((n, 8, 224, 224), np.float32)          # RGB zero-padded to 8 channels in memory
-    img[:, :3] = cc.normal((n, 3, 224, 224), 0, "cfg5/image")
+    img = cc.normal((n, 3, 224, 224), 0, "cfg5/image")    # a true 3-channel image
     pooled = np.abs(cc.normal((n, 64, 56, 56), 0, "cfg5/pooled"))
     return img, pooled
 
@@ -344,7 +343,12 @@ EDGE = [
     (1, 32, 23, 23, 32, 3, 3, 3, 4, 2, "gelu"),            # stride 3, large padding, dilation 2
     (1, 64, 32, 32, 64, 7, 7, 2, 3, 1, "bias+relu"),       # 7x7 / 2
     (5, 64, 7, 7, 2048, 1, 1, 1, 0, 1, "bias+relu"),       # wide output, tiny image
-    (2, 3, 37, 41, 64, 7, 7, 2, 3, 1, "bias+relu"),        # RGB stem: 16-byte pixels, filter rows fetched as windows
+    (2, 3, 37, 41, 64, 7, 7, 2, 3, 1, "bias+relu"),        # RGB stem: filter rows fetched as windows (16-bit: 8-byte
+                                                           # pixels, odd padded width; fp32: 16-byte pixels)
+    (2, 4, 20, 30, 16, 2, 8, (1, 2), (0, 3), 1, ""),       # 8-byte pixels, 8-wide filter row fills the whole window
+    (1, 2, 15, 40, 24, 3, 4, (1, 4), (1, 2), 1, "bias"),   # 8-byte pixels, horizontal stride 4 (two W units a step)
+    (2, 1, 30, 30, 8, 5, 5, 2, 2, 1, "relu"),              # single-channel image, 5x5 / 2
+    (1, 3, 64, 300, 32, 3, 3, 2, 1, 1, "bias+relu"),       # 8-byte pixels, rows wider than one tile
     (2, 8, 20, 30, 16, 2, 8, (1, 2), (0, 3), 1, ""),       # 8-wide filter row fills the whole window
     (2, 8, 20, 30, 16, 3, 9, 1, (1, 4), 1, ""),            # 9-wide filter: too wide for a window, per-tap path
     (2, 8, 21, 21, 16, 3, 3, 1, 2, (1, 2), "silu"),        # 16-byte pixels with horizontal dilation: per-tap path
@@ -619,3 +623,56 @@ def test_resident_filter_kernel_writes_strided_views_and_agrees_with_the_general
     assert float((a - g).abs().max()) <= 2.0 ** -7 * float(g.abs().max())
     want = run_oracle(x, w, b, None, 1, 1, 1, "bias+relu", "bf16")
     assert cc.rel_err(view.float().cpu().numpy(), want) <= cc.TOL_16BIT
+
+
+# --------------------------------------------------------------------------- row-band kernel (few-channel images)
+ROW_BAND = [
+    # N, C, H, W, K, R, S, stride, pad, dil, dtype, epilogue
+    (2, 3, 64, 230, 64, 7, 7, 2, 3, 1, "bf16", "bias+relu"),          # the RGB stem shape family: 4-channel pixels, stride 2
+    (3, 3, 224, 224, 64, 7, 7, 2, 3, 1, "f16", "bias+relu"),          # ResNet-50 conv1 itself
+    (2, 4, 20, 250, 16, 2, 8, (1, 2), (0, 3), 1, "bf16", ""),         # 8-wide filter row: both K slices full; K_out 16
+    (1, 8, 30, 120, 40, 3, 3, 1, 1, 1, "bf16", "bias+silu"),          # 8-channel pixels, stride 1; K_out 40: clipped stores
+    (1, 6, 18, 100, 64, 5, 5, 1, 2, 1, "f16", "gelu"),                # 6 channels padded to 8: three K slices per filter row
+    (1, 3, 20, 520, 32, 3, 3, 2, 1, 1, "bf16", "bias"),               # Wo = 260: three column tiles, the last one ragged
+    (1, 3, 40, 240, 24, 3, 5, (3, 2), (2, 2), (2, 1), "bf16", "relu"),   # vertical stride 3, vertical dilation 2
+    (5, 1, 33, 200, 8, 4, 6, (1, 2), (3, 2), 1, "bf16", "bias+relu"),    # one channel; more padding than the filter needs
+    (1, 3, 9, 224, 64, 7, 7, 2, 3, 1, "bf16", "bias+relu"),           # fewer output rows than a band holds
+]
+
+
+@pytest.mark.parametrize("case", ROW_BAND, ids=lambda c: "N%dC%dH%dW%dK%dR%dS%d" % c[:7])
+@pytest.mark.parametrize("channels_last", [True, False])
+def test_row_band_kernel_matches_the_oracle(case, channels_last):
+    """16-bit images of up to 8 channels whose horizontal step is 16 bytes of channel-padded input take the kernel
+    that keeps bands of input rows in shared memory and reads the im2col matrix through overlapping-row descriptors
+    (conv2d_rowband_sm100.cuh): full tensors against the oracle, from channels-last and from NCHW memory, and the
+    launch counter shows which kernel produced them."""
+    N, C, H, W, K, R, S, stride, pad, dil, dtype, epi = case
+    x = cc.normal((N, C, H, W), 8, "rb/x")
+    w = cc.kaiming((K, C, R, S), 8, "rb/w")
+    b = cc.normal((K,), 8, "rb/b", 0.1)
+    before = ffi.launch_count_of(ffi.KERNEL_ROW_BAND)
+    check(x, w, b, None, stride, pad, dil, epi, dtype, channels_last=channels_last, out_channels_last=True)
+    assert ffi.launch_count_of(ffi.KERNEL_ROW_BAND) == before + 1
+
+
+def test_row_band_kernel_agrees_with_the_general_kernel_on_a_zero_padded_image():
+    """The same RGB image stored with 8 channels (5 of them zero) does not qualify (stride 2 over 16-byte pixels) and
+    takes the general kernel: same values up to the summation order inside an MMA."""
+    n = 4
+    x = cc.normal((n, 3, 96, 224), 9, "rb2/x")
+    w = cc.kaiming((64, 3, 7, 7), 9, "rb2/w")
+    b = cc.normal((64,), 9, "rb2/b", 0.1)
+    x8 = np.zeros((n, 8, 96, 224), np.float32)
+    x8[:, :3] = x
+    w8 = np.zeros((64, 8, 7, 7), np.float32)
+    w8[:, :3] = w
+    tb = torch.from_numpy(b).cuda()
+    before = ffi.launch_count_of(ffi.KERNEL_ROW_BAND)
+    band = ops.conv2d_nchw(to_dev(x, "bf16"), to_dev(w, "bf16"), tb, None, 2, 3, 1, 1, "bias+relu")
+    assert ffi.launch_count_of(ffi.KERNEL_ROW_BAND) == before + 1
+    general = ops.conv2d_nchw(to_dev(x8, "bf16"), to_dev(w8, "bf16"), tb, None, 2, 3, 1, 1, "bias+relu")
+    assert ffi.launch_count_of(ffi.KERNEL_ROW_BAND) == before + 1
+    torch.cuda.synchronize()
+    a, g = band.float(), general.float()
+    assert float((a - g).abs().max()) <= 2.0 ** -7 * float(g.abs().max())

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtracea_b200.so")
 SOURCES = [os.path.join(CSRC, "tracea_ffi.cu")]
-HEADERS = [os.path.join(CSRC, f) for f in ("conv2d_sm100.cuh", "conv2d_window_sm100.cuh", "ptx_sm100.cuh", "layout_kernels.cuh")] + [
+HEADERS = [os.path.join(CSRC, f) for f in ("conv2d_sm100.cuh", "conv2d_window_sm100.cuh", "conv2d_rowband_sm100.cuh", "ptx_sm100.cuh", "layout_kernels.cuh")] + [
     os.path.join(HERE, "..", "include", "tracea_b200.h")]
 
 NVCC_FLAGS = [

@@ -69,7 +69,8 @@ __global__ void to_channels_last_wpad_kernel(const T* __restrict__ src, T* __res
     for (int c = 0; c < kCp; ++c)
       if (c < C) v[c] = p[c * sc];
   }
-  *reinterpret_cast<uint4*>(dst + i * kCp) = *reinterpret_cast<const uint4*>(v);
+  if constexpr (kCp * sizeof(T) == 16) *reinterpret_cast<uint4*>(dst + i * kCp) = *reinterpret_cast<const uint4*>(v);
+  else *reinterpret_cast<uint2*>(dst + i * kCp) = *reinterpret_cast<const uint2*>(v);   // 8-byte pixels (4 x 16 bit)
 }
 
 // w[k, c, r, s] (element strides) -> dst[k][r][s][Cp], zero-padded channels: the K-major B operand

@@ -112,6 +112,38 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// The same wait for a whole warp: lane 0 polls (optionally with a short sleep between polls), the other lanes park
+// at the shuffle that hands them the answer -- a value the compiler knows to be the same in every lane, so the code
+// that follows stays in uniform control flow. Callers follow with tcgen05.fence::after_thread_sync before touching
+// TMEM.
+template <bool kSleep = true>
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                       long long limit_cycles, int lane) {
+  uint32_t ok = 1u;
+  if (lane == 0 && !mbar_try_wait(bar, parity)) {
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+      if constexpr (kSleep) __nanosleep(64);
+      if (mbar_try_wait(bar, parity)) break;
+      if ((++spins & 0x3fu) == 0) {
+        if (*abort_flag != 0u || clock64() - t0 > limit_cycles) {
+          ok = 0u;
+          break;
+        }
+      }
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0u;
+}
+
+// One lane of a converged warp, as a 0 / 1 word (elect.sync).
+__device__ __forceinline__ uint32_t elect_one_lane() {
+  uint32_t pred;
+  asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}\n" : "=r"(pred));
+  return pred;
+}
+
 // ------------------------------------------------------------------ TMA loads (no multicast)
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -25,6 +25,7 @@
 #include "../../include/tracea_b200.h"
 #include "conv2d_sm100.cuh"
 #include "conv2d_window_sm100.cuh"
+#include "conv2d_rowband_sm100.cuh"
 #include "layout_kernels.cuh"
 
 namespace {
@@ -109,7 +110,7 @@ std::atomic<int> g_test_producer_stop{-1};
 std::atomic<bool> g_attr_set[kMaxDevices][3][3][9];
 std::atomic<unsigned long long> g_kernel_launches{0};   // every kernel this library has launched (conv + layout adapters)
 // the same, by kind: 0 general implicit-GEMM kernel, 1 its K-split instantiations, 2 resident-filter kernel, 3 layout adapters
-std::atomic<unsigned long long> g_launches_by_kind[4];
+std::atomic<unsigned long long> g_launches_by_kind[5];
 EncodeTiledFn g_encode_tiled = nullptr;
 EncodeIm2colFn g_encode_im2col = nullptr;
 
@@ -339,7 +340,7 @@ int env_int(const char* name, int dflt) {
 // part of the ~6 us a call costs on the host). TRACEA_B200_HOST_CHUNKS is read per call and is not in here.
 struct Knobs {
   int force_bn, force_stages, force_chunk, no_tma_store, no_tma_residual, tiled_a, force_staging, no_window,
-      pair, rows2, panel, pdl, split_k, no_window3;
+      pair, rows2, panel, pdl, split_k, no_window3, no_row_band;
 };
 const Knobs& knobs() {
   static const Knobs k = {
@@ -349,7 +350,8 @@ const Knobs& knobs() {
       env_int("TRACEA_B200_FORCE_STAGING", 0), env_int("TRACEA_B200_NO_WINDOW", 0),
       env_int("TRACEA_B200_PAIR", -1),         env_int("TRACEA_B200_ROWS2", -1),
       env_int("TRACEA_B200_PANEL", 0),         env_int("TRACEA_B200_PDL", 1),
-      env_int("TRACEA_B200_SPLIT_K", 0),       env_int("TRACEA_B200_NO_RESIDENT_FILTER", 0)};
+      env_int("TRACEA_B200_SPLIT_K", 0),       env_int("TRACEA_B200_NO_RESIDENT_FILTER", 0),
+      env_int("TRACEA_B200_NO_ROW_BAND", 0)};
   return k;
 }
 
@@ -600,6 +602,174 @@ struct CoreParams : TraceaConv2dParams {
 };
 
 // All pointers are device pointers on `dev`. x: [N,C,H,W], w: [K,C,R,S], out: [N,K,Ho,Wo] (logical).
+// ------------------------------------------------------------------ row-band kernel (few-channel images, e.g. the RGB stem)
+// Tries the kernel of conv2d_rowband_sm100.cuh: 16-bit images of up to 8 channels whose horizontal step is 16 bytes
+// of (channel-padded) input -- 4-channel pixels under stride_w 2, 8-channel pixels under stride_w 1. Stages the
+// padded channels-last copy of x and the packed filter bank itself (`staging` hands out the scratch), then launches.
+// Returns false (nothing launched, nothing staged) when the layer does not qualify.
+std::atomic<bool> g_rowband_attr_set[kMaxDevices][2];
+
+template <typename Staging>
+bool try_row_band_conv(DeviceState& st, Staging&& staging, const View4& x, const View4& w, const View4* bias,
+                       const View4& out, const CoreParams& p, const Epilogue& epi, cudaStream_t stream) {
+  const long long N = x.shape[0], C = x.shape[1], H = x.shape[2], W = x.shape[3];
+  const long long K = w.shape[0], R = w.shape[2], S = w.shape[3];
+  const long long Ho = out.shape[2], Wo = out.shape[3];
+  if (knobs().no_row_band != 0 || st.status == nullptr) return false;
+  if (x.dtype == TRACEA_DTYPE_FLOAT32 || C > 8 || K > 64 || (K % 8) != 0 || epi.residual) return false;
+  const long long Cw = C <= 4 ? 4 : 8;                     // channels per pixel of the padded copy
+  const long long px_bytes = Cw * 2;
+  if ((long long)p.stride_w * px_bytes != 16 || p.dilation_w != 1 || S < 2) return false;
+  const long long kmma = (S * px_bytes + 31) / 32;         // K = 16 MMAs per filter row
+  if (kmma > 4 || R > 16 || p.dilation_h > 8) return false;
+  const bool ovec = out.stride[1] == 1 && aligned16(out.ptr) && (out.stride[0] * 2) % 16 == 0 &&
+                    (out.stride[2] * 2) % 16 == 0 && (out.stride[3] * 2) % 16 == 0;
+  if (!ovec || N > 0x3fffffffLL / (Ho + 1)) return false;
+  // row pitch: the padded row, and at least what the last output pixel's taps (zero-weight ones included) read
+  const long long px_per_128 = 128 / px_bytes;
+  const long long need_px = std::max<long long>(W + p.padding_w + p.pad_w_hi, (Wo - 1) * p.stride_w + kmma * 32 / px_bytes);
+  const long long Wpitch = (need_px + px_per_128 - 1) / px_per_128 * px_per_128;
+  const long long row_bytes = Wpitch * px_bytes;
+  if (row_bytes / 128 > 256 || Wo < 32) return false;
+  const long long wtiles = (Wo + 127) / 128;
+  if (Wo * 100 < wtiles * 128 * 60) return false;          // mostly dropped rows: the general kernel packs pixels densely
+  const uint32_t w_bytes = static_cast<uint32_t>(R * kmma) * 2048u;
+
+  // band height: the cheapest of 16, 8, 4, 2, 1 output rows by a simple cycle model (MMA time + copy time, times
+  // the bands the busiest CTA gets); at least two slots must fit
+  long long hb = 0, best_cost = 0, in_rows = 0, slot_bytes = 0, num_slots = 0;
+  for (long long h = 16; h >= 1; h >>= 1) {
+    if (h > Ho && h > 1) continue;
+    const long long rows_in = (h - 1) * p.stride_h + (R - 1) * p.dilation_h + 1;
+    if (rows_in > 256) continue;
+    const long long slot = (rows_in * row_bytes + 2048 + 128 + 1023) / 1024 * 1024;
+    const long long fixed = tb200::rowband_smem_bytes(w_bytes, 0, 0);
+    const long long slots = std::min<long long>(tb200::kBandMaxSlots, (232448 - fixed) / slot);
+    if (slots < 2) continue;
+    const long long bands = N * ((Ho + h - 1) / h);
+    const long long ctas = std::min<long long>(bands, st.num_sms);
+    const long long per_cta = (bands + ctas - 1) / ctas;
+    const long long cost = per_cta * (h * wtiles * R * kmma * 55 + rows_in * row_bytes / 32);
+    if (hb == 0 || cost < best_cost) {
+      hb = h; best_cost = cost; in_rows = rows_in; slot_bytes = slot; num_slots = slots;
+    }
+  }
+  if (hb == 0) return false;
+  const long long bands_per_img = (Ho + hb - 1) / hb, n_bands = N * bands_per_img;
+  if (n_bands > 0x3fffffffLL) return false;
+
+  // ---- staging: the padded channels-last copy of x, the packed filter bank
+  Scratch x_scratch, w_scratch;
+  const long long pixels = N * H * Wpitch;
+  void* x_stage = staging(x_scratch, static_cast<size_t>(pixels * px_bytes), "the padded channels-last copy of x");
+  {
+    const int threads = 256;
+    const unsigned blocks = static_cast<unsigned>((pixels + threads - 1) / threads);
+    if (Cw == 4)
+      tb200::to_channels_last_wpad_kernel<uint16_t, 4><<<blocks, threads, 0, stream>>>(
+          static_cast<const uint16_t*>(x.ptr), static_cast<uint16_t*>(x_stage), (int)C, (int)H, (int)W, (int)Wpitch,
+          (int)p.padding_w, pixels, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
+    else
+      tb200::to_channels_last_wpad_kernel<uint16_t, 8><<<blocks, threads, 0, stream>>>(
+          static_cast<const uint16_t*>(x.ptr), static_cast<uint16_t*>(x_stage), (int)C, (int)H, (int)W, (int)Wpitch,
+          (int)p.padding_w, pixels, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
+    TB_CUDA(cudaGetLastError());
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    g_launches_by_kind[3].fetch_add(1, std::memory_order_relaxed);
+  }
+  const long long Sd = kmma * 32 / px_bytes;               // tap slots per filter row in the packed bank
+  void* w_stage = staging(w_scratch, static_cast<size_t>(K * R * Sd * px_bytes), "the packed filter bank");
+  launch_weight_pack(w.ptr, w_stage, 2, K, C, R, S, Sd, Cw, w.stride, stream);
+
+  CUtensorMap tmap_x;
+  {
+    const cuuint64_t gdim[4] = {64, (cuuint64_t)(row_bytes / 128), (cuuint64_t)H, (cuuint64_t)N};
+    const cuuint64_t gstr[3] = {128, (cuuint64_t)row_bytes, (cuuint64_t)(H * row_bytes)};
+    const cuuint32_t box[4] = {64u, (cuuint32_t)(row_bytes / 128), (cuuint32_t)in_rows, 1u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = g_encode_tiled(&tmap_x, tmap_dtype(x.dtype), 4, x_stage, gdim, gstr, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled (row band) failed with %d", (int)r);
+  }
+  CUtensorMap tmap_out;
+  {
+    // the output as {channel, column, row, image}; a warp stores 32 pixels x 64 channels, clipped at Wo and K_out
+    const cuuint64_t gdim[4] = {(cuuint64_t)K, (cuuint64_t)Wo, (cuuint64_t)Ho, (cuuint64_t)N};
+    const cuuint64_t gstr[3] = {(cuuint64_t)(out.stride[3] * 2), (cuuint64_t)(out.stride[2] * 2),
+                                (cuuint64_t)(out.stride[0] * 2)};
+    const cuuint32_t box[4] = {64u, 32u, 1u, 1u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = g_encode_tiled(&tmap_out, tmap_dtype(out.dtype), 4, out.ptr, gdim, gstr, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TB_FAIL(TRACEA_CUDA_ERROR, "cuTensorMapEncodeTiled (row band output) failed with %d", (int)r);
+  }
+
+  tb200::RowBandKernelArgs a;
+  memset(&a, 0, sizeof(a));
+  a.R = (int)R; a.stride_h = (int)p.stride_h; a.pad_h = (int)p.padding_h; a.dil_h = (int)p.dilation_h;
+  a.Ho = (int)Ho; a.Wo = (int)Wo;
+  a.hb = (int)hb; a.bands_per_img = (int)bands_per_img; a.n_bands = (int)n_bands;
+  a.wtiles = (int)wtiles; a.kmma = (int)kmma; a.num_slots = (int)num_slots;
+  a.row_bytes = static_cast<uint32_t>(row_bytes);
+  a.box_bytes = static_cast<uint32_t>(in_rows * row_bytes);
+  a.slot_bytes = static_cast<uint32_t>(slot_bytes);
+  a.w_bytes = w_bytes;
+  a.idesc = tb200::ptx::make_idesc(x.dtype == TRACEA_DTYPE_FLOAT16 ? 0u : 1u, 128, tb200::kBandBN);
+  a.w = w_stage;
+  a.K_out = (int)K;
+  if (epi.bias && bias != nullptr) {
+    a.bias = bias->ptr;
+    a.bias_is_f32 = bias->dtype == TRACEA_DTYPE_FLOAT32 ? 1 : 0;
+  }
+  a.act = epi.act;
+  a.status = st.status;
+  {
+    const long long lim = g_test_wait_limit.load(std::memory_order_relaxed);
+    a.wait_limit = lim > 0 ? lim : tb200::kWaitLimitCycles;
+    a.test_producer_stop = g_test_producer_stop.load(std::memory_order_relaxed);
+  }
+
+#ifdef TB200_PROFILE
+  {
+    const char* pp = getenv("TRACEA_B200_PROF_PTR");
+    a.prof = pp != nullptr ? reinterpret_cast<long long*>(strtoull(pp, nullptr, 0)) : nullptr;
+  }
+#endif
+  const int smem = static_cast<int>(tb200::rowband_smem_bytes(w_bytes, a.slot_bytes, a.num_slots));
+  const int grid = static_cast<int>(std::min<long long>(n_bands, st.num_sms));
+  const bool bf16 = x.dtype == TRACEA_DTYPE_BFLOAT16;
+  auto kern_bf = tb200::conv2d_rowband_sm100_kernel<__nv_bfloat16>;
+  auto kern_h = tb200::conv2d_rowband_sm100_kernel<__half>;
+  std::atomic<bool>& attr_done = g_rowband_attr_set[st.dev][bf16 ? 0 : 1];
+  if (!attr_done.load(std::memory_order_relaxed)) {
+    if (bf16) TB_CUDA(cudaFuncSetAttribute(kern_bf, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    else TB_CUDA(cudaFuncSetAttribute(kern_h, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    attr_done.store(true, std::memory_order_relaxed);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(tb200::kBandThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  unsigned n_attr = 0;
+  if (knobs().pdl != 0) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
+  if (bf16) TB_CUDA(cudaLaunchKernelEx(&cfg, kern_bf, tmap_x, tmap_out, a));
+  else TB_CUDA(cudaLaunchKernelEx(&cfg, kern_h, tmap_x, tmap_out, a));
+  TB_CUDA(cudaGetLastError());
+  g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+  g_launches_by_kind[4].fetch_add(1, std::memory_order_relaxed);
+  return true;
+}
+
 void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const View4& w_in, const View4* bias,
                  const View4* residual, const View4& out, const CoreParams& p, const Epilogue& epi);
 
@@ -807,6 +977,9 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
 
   const int vec_elems = 16 / es;
   const long long Cp = (C + vec_elems - 1) / vec_elems * vec_elems;
+
+  // ---- few-channel 16-bit images with a 16-byte horizontal step: the row-band kernel reads them in place
+  if (C <= 8 && es == 2 && try_row_band_conv(st, staging, x_in, w_in, bias, out, p, epi, stream)) return;
 
   // ---- small-channel inputs (a pixel is 16 bytes after channel padding, e.g. the RGB stem): copy x with the
   // horizontal padding materialised; one filter row of a pixel is then 8 adjacent pixels = one 128-byte
@@ -1966,7 +2139,7 @@ void tracea_b200_test_hooks(int64_t wait_limit_cycles, int32_t producer_stop_aft
 uint64_t tracea_b200_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 uint64_t tracea_b200_launch_count_of(int32_t kind) {
-  if (kind < 0 || kind >= 4) return 0;
+  if (kind < 0 || kind >= 5) return 0;
   return g_launches_by_kind[kind].load(std::memory_order_relaxed);
 }
 

@@ -217,7 +217,7 @@ def conv_transpose2d_raw(x, w, bias, residual, out, stride=(1, 1), padding=(0, 0
     return st
 
 
-KERNEL_GENERAL, KERNEL_SPLIT_K, KERNEL_RESIDENT_FILTER, KERNEL_LAYOUT = range(4)
+KERNEL_GENERAL, KERNEL_SPLIT_K, KERNEL_RESIDENT_FILTER, KERNEL_LAYOUT, KERNEL_ROW_BAND = range(5)
 
 
 def launch_count_of(kind):

@@ -42,8 +42,11 @@ class ConvStack:
                 fan_in = sp.C * sp.R * sp.S
                 w = torch.randn((sp.K, sp.C, sp.R, sp.S), generator=gen) * (2.0 / fan_in) ** 0.5
                 b = torch.randn((sp.K,), generator=gen) * 0.05
-            c_phys = sp.C if sp.C % 8 == 0 else (sp.C + 7) // 8 * 8
-            if c_phys != sp.C:  # e.g. the RGB stem: channels are zero-padded in memory, 3 -> 8
+            # an input supplied with more channels than the layer reads (an RGB image stored with zero-padded
+            # channels) gets weights padded to match; a true 3-channel image is taken as it is
+            src = self.tensors.get(sp.src)
+            c_phys = src.shape[1] if src is not None and src.shape[1] > sp.C else sp.C
+            if c_phys != sp.C:
                 wp = torch.zeros((sp.K, c_phys, sp.R, sp.S))
                 wp[:, :sp.C] = w
                 w = wp
