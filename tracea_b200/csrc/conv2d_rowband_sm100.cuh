@@ -268,7 +268,7 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
         const int ho0 = (b % args.bands_per_img) * args.hb;
         const int rows = min(args.hb, args.Ho - ho0);
         TB200_PROF_T(tw1);
-        if (!mbar_wait_bounded_warp<false>(band_full(slot), use & 1u, abort_p, args.wait_limit, lane)) {
+        if (!mbar_wait_bounded_uniform(band_full(slot), use & 1u, abort_p, args.wait_limit)) {
           if (issue) report_error_status(args.status, abort_p, kErrMmaWaitFull, it);
           ok = false;
           break;
@@ -282,7 +282,7 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
           for (int wt = 0; wt < args.wtiles; ++wt, ++unit, a_unit += 128u) {
             // accumulator `buf` is free once its previous drain (the use before this one) has arrived
             TB200_PROF_T(tw0);
-            if (!acc_free && !mbar_wait_bounded_warp<false>(tempty_bar(buf), buf_parity ^ 1u, abort_p, args.wait_limit, lane)) {
+            if (!acc_free && !mbar_wait_bounded_uniform(tempty_bar(buf), buf_parity ^ 1u, abort_p, args.wait_limit)) {
               if (issue) report_error_status(args.status, abort_p, kErrMmaWaitTmem, unit);
               ok = false;
               break;
@@ -293,7 +293,7 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             const uint32_t d = tmem_base + buf * kBandBN;
             const uint32_t commit_bar = tfull_bar(buf);
             if (++buf == kBandAccs) { buf = 0; buf_parity ^= 1u; }
-            const uint32_t probe = mbar_test_wait(tempty_bar(buf), buf_parity ^ 1u) ? 1u : 0u;
+            const bool probe = mbar_test_wait(tempty_bar(buf), buf_parity ^ 1u);
             uint32_t a_row = a_unit;
             uint32_t b_lo = b_first;
             uint32_t acc = 0u;
@@ -318,7 +318,7 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             }
             TB200_PROF_ADD(prof_loop, tl);
             if (issue) mma_commit(commit_bar);   // this accumulator is complete
-            acc_free = __shfl_sync(0xffffffffu, probe, 0) != 0u;
+            acc_free = __all_sync(0xffffffffu, probe);
           }
         }
         if (issue) mma_commit(band_empty(slot));     // the band may be overwritten

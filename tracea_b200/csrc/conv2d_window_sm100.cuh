@@ -86,36 +86,40 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
 // The four K = 16 MMAs of one filter tap (64 channels) as a single block: M = 256 over a CTA pair, kind::f16 (fp16 /
 // bf16 operands, fp32 accumulate). a_lo / b_lo are descriptor low words of the first K slice; the others follow 32
 // bytes (2 units) apart inside the 128-byte rows. kFirstAccumulates = false: the first MMA overwrites the accumulator.
+// Executed by the whole (converged) MMA warp with identical operands in every lane; the instructions are predicated
+// on `issue`, 1 in one lane: operand arithmetic in uniform control flow stays in uniform registers, where the MMA
+// reads its descriptors from, and that is what lets one warp feed N = 64 MMAs at the tensor pipe's pace.
 template <bool kFirstAccumulates>
 __device__ __forceinline__ void mma_tap4_pair(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
-                                              uint32_t idesc) {
+                                              uint32_t idesc, uint32_t issue) {
   asm volatile(
       "{\n"
-      ".reg .pred p0, p1;\n"
+      ".reg .pred p0, p1, q;\n"
       ".reg .b64 da, db;\n"
       ".reg .b32 a, b;\n"
       "setp.ne.b32 p0, %5, 0;\n"
       "setp.eq.b32 p1, 0, 0;\n"
+      "setp.ne.b32 q, %6, 0;\n"
       "mov.b64 da, {%1, %3};\n"
       "mov.b64 db, {%2, %3};\n"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p0;\n"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p0;\n"
       "add.u32 a, %1, 2;\n"
       "add.u32 b, %2, 2;\n"
       "mov.b64 da, {a, %3};\n"
       "mov.b64 db, {b, %3};\n"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p1;\n"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p1;\n"
       "add.u32 a, %1, 4;\n"
       "add.u32 b, %2, 4;\n"
       "mov.b64 da, {a, %3};\n"
       "mov.b64 db, {b, %3};\n"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p1;\n"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p1;\n"
       "add.u32 a, %1, 6;\n"
       "add.u32 b, %2, 6;\n"
       "mov.b64 da, {a, %3};\n"
       "mov.b64 db, {b, %3};\n"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p1;\n"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p1;\n"
       "}\n" ::"r"(tmem_d),
-      "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(kFirstAccumulates ? 1 : 0)
+      "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(kFirstAccumulates ? 1 : 0), "r"(issue)
       : "memory");
 }
 }  // namespace ptx
@@ -153,7 +157,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
   static_assert(sizeof(OutT) == 2, "16-bit activations only");
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kBufCols = kWinMaxBlocks * kWinBN;   // 256 columns per accumulator buffer
-  const uint32_t cta_rank = cluster_ctarank();
+  const uint32_t cta_rank = __shfl_sync(0xffffffffu, cluster_ctarank(), 0);   // the same in every lane, provably
   const bool leader = cta_rank == 0u;
   const int pair = static_cast<int>(blockIdx.x >> 1);
   const int num_pairs = static_cast<int>(gridDim.x >> 1);
@@ -177,7 +181,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
   volatile uint32_t* abort_p = tmem_slot_p + 1;
   float* bias_s = reinterpret_cast<float*>(smem_gen + bias_off);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // likewise
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -205,7 +209,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
   tc_fence_before();
   cluster_sync();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot_p;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot_p, 0);
   griddep_launch_dependents();
   griddep_wait();
   TB200_PROF_NOW(13);
@@ -280,57 +284,81 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (one thread of the leader CTA)
-    if (lane == 0 && leader) {
+    // ------------------------------------------------------------ MMA issuer (warp 1 of the leader CTA; one lane issues)
+    if (leader) {
+      const uint32_t issue = elect_one_lane();
       const uint32_t desc_hi = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);   // SBO 1024 B, SWIZZLE_128B
-      bool ok = mbar_wait_bounded(w_bar, 0u, abort_p, args.wait_limit);
-      if (!ok) report_error_status(args.status, abort_p, kErrMmaWaitFull, 0xffffu);
+      bool ok = mbar_wait_bounded_uniform(w_bar, 0u, abort_p, args.wait_limit);
+      if (!ok && issue) report_error_status(args.status, abort_p, kErrMmaWaitFull, 0xffffu);
       uint32_t it = 0;
-      long long prof_wfull = 0, prof_wtmem = 0;
-      (void)prof_wfull; (void)prof_wtmem;
+      long long prof_wfull = 0, prof_wtmem = 0, prof_loop = 0;
+      (void)prof_wfull; (void)prof_wtmem; (void)prof_loop;
       TB200_PROF_T(prof_t0);
+      const uint32_t w_units = w_s >> 4;
+      const uint32_t row_step = static_cast<uint32_t>(args.Wp - args.S) * 8u;   // from the last tap of a filter row to the next row
+      const uint32_t row_units = static_cast<uint32_t>(args.Wp) * 8u;          // one window row, in 16-byte units
+      const uint32_t idesc = args.idesc;
+      const bool three_by_three = args.R == 3 && args.S == 3;
       for (int j = pair; j < args.pair_tiles && ok; j += num_pairs, ++it) {
         const uint32_t slot = it & 1u, use = it >> 1;   // window slot and accumulator buffer alternate together
         const int nblk = j < args.pair_tiles_full ? args.nblk_full : args.nblk_short;
         TB200_PROF_T(tw0);
-        if (!mbar_wait_bounded(tempty_bar(slot), (use & 1u) ^ 1u, abort_p, args.wait_limit)) {
-          report_error_status(args.status, abort_p, kErrMmaWaitTmem, it);
+        if (!mbar_wait_bounded_uniform(tempty_bar(slot), (use & 1u) ^ 1u, abort_p, args.wait_limit)) {
+          if (issue) report_error_status(args.status, abort_p, kErrMmaWaitTmem, it);
           ok = false;
           break;
         }
         TB200_PROF_ADD(prof_wtmem, tw0);
         TB200_PROF_T(tw1);
-        if (!mbar_wait_bounded(win_full(slot), use & 1u, abort_p, args.wait_limit)) {
-          report_error_status(args.status, abort_p, kErrMmaWaitFull, it);
+        if (!mbar_wait_bounded_uniform(win_full(slot), use & 1u, abort_p, args.wait_limit)) {
+          if (issue) report_error_status(args.status, abort_p, kErrMmaWaitFull, it);
           ok = false;
           break;
         }
         TB200_PROF_ADD(prof_wfull, tw1);
         tc_fence_after();
         const uint32_t win_units = (win_s + slot * args.slot_bytes) >> 4;   // 16-byte units: 8 per 128-byte pixel row
-        const uint32_t w_units = w_s >> 4;
-        const uint32_t row_step = static_cast<uint32_t>(args.Wp - args.S) * 8u;   // from the last tap of a filter row to the next row
+        TB200_PROF_T(tl);
         for (int blk = 0; blk < nblk; ++blk) {
           const uint32_t d = tmem_base + slot * kBufCols + static_cast<uint32_t>(blk) * kWinBN;
           // tap (r, s) reads the window shifted by r * Wp + s pixel rows; walked incrementally
           uint32_t a_lo = win_units + static_cast<uint32_t>(blk) * (128u * 8u);
           uint32_t b_lo = w_units;
-          mma_tap4_pair<false>(d, a_lo, b_lo, desc_hi, args.idesc);
+          if (three_by_three) {   // the common filter, as straight-line code
+            mma_tap4_pair<false>(d, a_lo, b_lo, desc_hi, idesc, issue);
+            mma_tap4_pair<true>(d, a_lo + 8u, b_lo + 256u, desc_hi, idesc, issue);
+            mma_tap4_pair<true>(d, a_lo + 16u, b_lo + 512u, desc_hi, idesc, issue);
+            mma_tap4_pair<true>(d, a_lo + row_units, b_lo + 768u, desc_hi, idesc, issue);
+            mma_tap4_pair<true>(d, a_lo + row_units + 8u, b_lo + 1024u, desc_hi, idesc, issue);
+            mma_tap4_pair<true>(d, a_lo + row_units + 16u, b_lo + 1280u, desc_hi, idesc, issue);
+            mma_tap4_pair<true>(d, a_lo + 2u * row_units, b_lo + 1536u, desc_hi, idesc, issue);
+            mma_tap4_pair<true>(d, a_lo + 2u * row_units + 8u, b_lo + 1792u, desc_hi, idesc, issue);
+            mma_tap4_pair<true>(d, a_lo + 2u * row_units + 16u, b_lo + 2048u, desc_hi, idesc, issue);
+            continue;
+          }
+          mma_tap4_pair<false>(d, a_lo, b_lo, desc_hi, args.idesc, issue);
           for (int r = 0; r < args.R; ++r) {
             for (int s = (r == 0 ? 1 : 0); s < args.S; ++s) {
               a_lo += 8u;
               b_lo += 256u;
-              mma_tap4_pair<true>(d, a_lo, b_lo, desc_hi, args.idesc);
+              mma_tap4_pair<true>(d, a_lo, b_lo, desc_hi, args.idesc, issue);
             }
             a_lo += row_step;
           }
         }
-        mma_commit_pair(win_empty(slot));   // the window may be overwritten (both CTAs)
-        mma_commit_pair(tfull_bar(slot));   // the accumulators are complete (both CTAs)
+        TB200_PROF_ADD(prof_loop, tl);
+        if (issue) {
+          mma_commit_pair(win_empty(slot));   // the window may be overwritten (both CTAs)
+          mma_commit_pair(tfull_bar(slot));   // the accumulators are complete (both CTAs)
+        }
+        __syncwarp();
       }
-      TB200_PROF_STORE(2, prof_wfull);
-      TB200_PROF_STORE(3, prof_wtmem);
-      TB200_PROF_STORE(4, clock64() - prof_t0);
+      if (issue) {
+        TB200_PROF_STORE(2, prof_wfull);
+        TB200_PROF_STORE(3, prof_wtmem);
+        TB200_PROF_STORE(6, prof_loop);
+        TB200_PROF_STORE(4, clock64() - prof_t0);
+      }
     }
   } else {
     // ------------------------------------------------------------ epilogue warps (2..9)
