@@ -23,7 +23,7 @@
 
 namespace tb200 {
 
-constexpr int kWinThreads = 320;        // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two groups of four)
+constexpr int kWinThreads = 352;        // warp 0 TMA, warps 1 and 10 MMA, warps 2..9 epilogue (two groups of four)
 constexpr int kWinBN = 64;              // output channels per MMA (K_out <= 64)
 constexpr int kWinMaxBlocks = 4;        // 128-pixel blocks per tile: 4 x 64 TMEM columns, double-buffered = 512
 constexpr int kWinStageBytes = 32 * 64; // per epilogue warp: 32 pixels x 64 bytes (half of the 64 channels)
@@ -124,6 +124,45 @@ __device__ __forceinline__ void mma_tap4_pair(uint32_t tmem_d, uint32_t a_lo, ui
 }
 }  // namespace ptx
 
+// The MMAs of one tile: for each of its `nblk` 128-pixel blocks (accumulators 64 TMEM columns apart), every filter
+// tap (r, s) reads the window shifted by r * Wp + s pixel rows (8 descriptor units each) against the tap's 4 KB of
+// the filter bank. k3x3: the common 3x3 filter as straight-line code. Whole-warp code, see mma_tap4_pair. Feeding
+// N = 64 MMAs is bound by how fast a warp gets through this instruction stream (about 65 cycles per MMA here against
+// the 43 the tensor pipe needs), so two warps issue, one block each in turn.
+template <bool k3x3>
+__device__ __forceinline__ void window_issue_tile(uint32_t tmem_d0, uint32_t win_units, uint32_t w_units,
+                                                  uint32_t desc_hi, uint32_t idesc, int blk0, int nblk, int R, int S,
+                                                  uint32_t row_units, uint32_t issue) {
+  using namespace ptx;
+  for (int blk = blk0; blk < nblk; blk += 2) {   // the two issuing warps take every second block
+    const uint32_t d = tmem_d0 + static_cast<uint32_t>(blk) * kWinBN;
+    uint32_t a_lo = win_units + static_cast<uint32_t>(blk) * (128u * 8u);
+    uint32_t b_lo = w_units;
+    if constexpr (k3x3) {
+      mma_tap4_pair<false>(d, a_lo, b_lo, desc_hi, idesc, issue);
+      mma_tap4_pair<true>(d, a_lo + 8u, b_lo + 256u, desc_hi, idesc, issue);
+      mma_tap4_pair<true>(d, a_lo + 16u, b_lo + 512u, desc_hi, idesc, issue);
+      mma_tap4_pair<true>(d, a_lo + row_units, b_lo + 768u, desc_hi, idesc, issue);
+      mma_tap4_pair<true>(d, a_lo + row_units + 8u, b_lo + 1024u, desc_hi, idesc, issue);
+      mma_tap4_pair<true>(d, a_lo + row_units + 16u, b_lo + 1280u, desc_hi, idesc, issue);
+      mma_tap4_pair<true>(d, a_lo + 2u * row_units, b_lo + 1536u, desc_hi, idesc, issue);
+      mma_tap4_pair<true>(d, a_lo + 2u * row_units + 8u, b_lo + 1792u, desc_hi, idesc, issue);
+      mma_tap4_pair<true>(d, a_lo + 2u * row_units + 16u, b_lo + 2048u, desc_hi, idesc, issue);
+    } else {
+      const uint32_t row_step = row_units - static_cast<uint32_t>(S) * 8u;   // from a filter row's last tap to the next row
+      mma_tap4_pair<false>(d, a_lo, b_lo, desc_hi, idesc, issue);
+      for (int r = 0; r < R; ++r) {
+        for (int s = (r == 0 ? 1 : 0); s < S; ++s) {
+          a_lo += 8u;
+          b_lo += 256u;
+          mma_tap4_pair<true>(d, a_lo, b_lo, desc_hi, idesc, issue);
+        }
+        a_lo += row_step;
+      }
+    }
+  }
+}
+
 // Staging box of one epilogue warp (32 pixel rows x 64 bytes; 16-byte chunk c of row r at
 // r*64 + ((c ^ ((r >> 1) & 3)) << 4): conflict-free both for a lane writing its own row and for the read-out
 // below) -> global memory. Lane l moves chunk l & 3 of rows (l >> 2) + 8 i, so every store instruction covers eight
@@ -188,8 +227,8 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
     mbar_init(w_bar, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(win_full(s), 1);
-      mbar_init(win_empty(s), 1);
-      mbar_init(tfull_bar(s), 1);
+      mbar_init(win_empty(s), 2);     // both MMA-issuing warps commit
+      mbar_init(tfull_bar(s), 2);
       mbar_init(tempty_bar(s), 16);   // the eight epilogue warps of both CTAs
     }
     *abort_p = 0u;
@@ -283,9 +322,10 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
         while (clock64() - t0 < 2000000LL) { __nanosleep(1000); }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (warp 1 of the leader CTA; one lane issues)
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------------------------ MMA issuers (warps 1 and 10 of the leader CTA; one lane issues)
     if (leader) {
+      const int issuer = warp == 1 ? 0 : 1;
       const uint32_t issue = elect_one_lane();
       const uint32_t desc_hi = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);   // SBO 1024 B, SWIZZLE_128B
       bool ok = mbar_wait_bounded_uniform(w_bar, 0u, abort_p, args.wait_limit);
@@ -295,7 +335,6 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
       (void)prof_wfull; (void)prof_wtmem; (void)prof_loop;
       TB200_PROF_T(prof_t0);
       const uint32_t w_units = w_s >> 4;
-      const uint32_t row_step = static_cast<uint32_t>(args.Wp - args.S) * 8u;   // from the last tap of a filter row to the next row
       const uint32_t row_units = static_cast<uint32_t>(args.Wp) * 8u;          // one window row, in 16-byte units
       const uint32_t idesc = args.idesc;
       const bool three_by_three = args.R == 3 && args.S == 3;
@@ -317,35 +356,15 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
         }
         TB200_PROF_ADD(prof_wfull, tw1);
         tc_fence_after();
-        const uint32_t win_units = (win_s + slot * args.slot_bytes) >> 4;   // 16-byte units: 8 per 128-byte pixel row
+        // (the shuffles restate that these are the same in every lane, whatever the loop around them looks like)
+        const uint32_t win_units = __shfl_sync(0xffffffffu, (win_s + slot * args.slot_bytes) >> 4, 0);   // 16-byte units
+        const uint32_t tile_d = __shfl_sync(0xffffffffu, tmem_base + slot * kBufCols, 0);
         TB200_PROF_T(tl);
-        for (int blk = 0; blk < nblk; ++blk) {
-          const uint32_t d = tmem_base + slot * kBufCols + static_cast<uint32_t>(blk) * kWinBN;
-          // tap (r, s) reads the window shifted by r * Wp + s pixel rows; walked incrementally
-          uint32_t a_lo = win_units + static_cast<uint32_t>(blk) * (128u * 8u);
-          uint32_t b_lo = w_units;
-          if (three_by_three) {   // the common filter, as straight-line code
-            mma_tap4_pair<false>(d, a_lo, b_lo, desc_hi, idesc, issue);
-            mma_tap4_pair<true>(d, a_lo + 8u, b_lo + 256u, desc_hi, idesc, issue);
-            mma_tap4_pair<true>(d, a_lo + 16u, b_lo + 512u, desc_hi, idesc, issue);
-            mma_tap4_pair<true>(d, a_lo + row_units, b_lo + 768u, desc_hi, idesc, issue);
-            mma_tap4_pair<true>(d, a_lo + row_units + 8u, b_lo + 1024u, desc_hi, idesc, issue);
-            mma_tap4_pair<true>(d, a_lo + row_units + 16u, b_lo + 1280u, desc_hi, idesc, issue);
-            mma_tap4_pair<true>(d, a_lo + 2u * row_units, b_lo + 1536u, desc_hi, idesc, issue);
-            mma_tap4_pair<true>(d, a_lo + 2u * row_units + 8u, b_lo + 1792u, desc_hi, idesc, issue);
-            mma_tap4_pair<true>(d, a_lo + 2u * row_units + 16u, b_lo + 2048u, desc_hi, idesc, issue);
-            continue;
-          }
-          mma_tap4_pair<false>(d, a_lo, b_lo, desc_hi, args.idesc, issue);
-          for (int r = 0; r < args.R; ++r) {
-            for (int s = (r == 0 ? 1 : 0); s < args.S; ++s) {
-              a_lo += 8u;
-              b_lo += 256u;
-              mma_tap4_pair<true>(d, a_lo, b_lo, desc_hi, args.idesc, issue);
-            }
-            a_lo += row_step;
-          }
-        }
+        if (three_by_three)
+          window_issue_tile<true>(tile_d, win_units, w_units, desc_hi, idesc, issuer, nblk, 3, 3, row_units, issue);
+        else
+          window_issue_tile<false>(tile_d, win_units, w_units, desc_hi, idesc, issuer, nblk, args.R, args.S, row_units,
+                                   issue);
         TB200_PROF_ADD(prof_loop, tl);
         if (issue) {
           mma_commit_pair(win_empty(slot));   // the window may be overwritten (both CTAs)
@@ -353,7 +372,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
         }
         __syncwarp();
       }
-      if (issue) {
+      if (issue && issuer == 0) {
         TB200_PROF_STORE(2, prof_wfull);
         TB200_PROF_STORE(3, prof_wtmem);
         TB200_PROF_STORE(6, prof_loop);
