@@ -28,7 +28,7 @@
 
 namespace tb200 {
 
-constexpr int kBandThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two groups of four)
+constexpr int kBandThreads = 352;   // warp 0 TMA, warps 1 and 10 MMA, warps 2..9 epilogue (two groups of four)
 constexpr int kBandBN = 64;         // output channels per MMA (K_out <= 64)
 constexpr int kBandAccs = 8;        // 64-column accumulators in TMEM
 constexpr int kBandMaxSlots = 4;    // band slots in shared memory
@@ -160,7 +160,7 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < kBandMaxSlots; ++s) {
       mbar_init(band_full(s), 1);
-      mbar_init(band_empty(s), 1);
+      mbar_init(band_empty(s), 2);   // both MMA-issuing warps commit
     }
     for (uint32_t b = 0; b < kBandAccs; ++b) {
       mbar_init(tfull_bar(b), 1);
@@ -247,9 +247,12 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
         while (clock64() - t0 < 2000000LL) { __nanosleep(1000); }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (the whole warp, one lane issues)
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------------------------ MMA issuers (two whole warps, one lane of each issues)
+    // Feeding N = 64 MMAs is bound by how fast a warp gets through the issuing instruction stream, so two warps
+    // issue: warp 1 the even units, warp 10 the odd ones -- the accumulators the epilogue group of the same parity drains.
     {
+      const uint32_t issuer = warp == 1 ? 0u : 1u;
       const uint32_t issue = elect_one_lane();
       const uint32_t desc_hi = (128u >> 4) | (1u << 14);        // SBO 128 B between 8-row groups, no swizzle
       const uint32_t a_lbo = (16u >> 4) << 16;                  // A: k-cores 16 B apart -- the overlapping rows
@@ -259,7 +262,7 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       const uint32_t b_step = static_cast<uint32_t>(args.kmma) * 128u;
       const uint32_t j_step = static_cast<uint32_t>(args.stride_h) * row_units;
       const uint32_t b_first = (w_s >> 4) | b_lbo;
-      uint32_t slot = 0, use = 0, unit = 0, it = 0, buf = 0, buf_parity = 0;   // buf_parity: parity of the use of `buf` now due
+      uint32_t slot = 0, use = 0, unit = 0, it = 0;
       bool ok = true, acc_free = false;
       long long prof_wfull = 0, prof_wtmem = 0, prof_loop = 0;
       (void)prof_wfull; (void)prof_wtmem; (void)prof_loop;
@@ -280,7 +283,9 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
         for (int j = 0; j < rows && ok; ++j, a_j += j_step) {
           uint32_t a_unit = a_j;
           for (int wt = 0; wt < args.wtiles; ++wt, ++unit, a_unit += 128u) {
+            if ((unit & 1u) != issuer) continue;
             // accumulator `buf` is free once its previous drain (the use before this one) has arrived
+            const uint32_t buf = unit & (kBandAccs - 1), buf_parity = (unit / kBandAccs) & 1u;
             TB200_PROF_T(tw0);
             if (!acc_free && !mbar_wait_bounded_uniform(tempty_bar(buf), buf_parity ^ 1u, abort_p, args.wait_limit)) {
               if (issue) report_error_status(args.status, abort_p, kErrMmaWaitTmem, unit);
@@ -289,11 +294,11 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             }
             TB200_PROF_ADD(prof_wtmem, tw0);
             tc_fence_after();
-            // ask about the next accumulator now; the answer comes back while this unit's MMAs are issued
+            // ask about this warp's next accumulator now; the answer comes back while this unit's MMAs are issued
             const uint32_t d = tmem_base + buf * kBandBN;
             const uint32_t commit_bar = tfull_bar(buf);
-            if (++buf == kBandAccs) { buf = 0; buf_parity ^= 1u; }
-            const bool probe = mbar_test_wait(tempty_bar(buf), buf_parity ^ 1u);
+            const uint32_t nbuf = (unit + 2u) & (kBandAccs - 1), nparity = ((unit + 2u) / kBandAccs) & 1u;
+            const bool probe = mbar_test_wait(tempty_bar(nbuf), nparity ^ 1u);
             uint32_t a_row = a_unit;
             uint32_t b_lo = b_first;
             uint32_t acc = 0u;
@@ -325,7 +330,7 @@ conv2d_rowband_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
         __syncwarp();
         if (++slot == static_cast<uint32_t>(args.num_slots)) { slot = 0; ++use; }
       }
-      if (issue) {
+      if (issue && issuer == 0u) {
         TB200_PROF_STORE(2, prof_wfull);
         TB200_PROF_STORE(3, prof_wtmem);
         TB200_PROF_STORE(6, prof_loop);

@@ -73,6 +73,29 @@ __global__ void to_channels_last_wpad_kernel(const T* __restrict__ src, T* __res
   else *reinterpret_cast<uint2*>(dst + i * kCp) = *reinterpret_cast<const uint2*>(v);   // 8-byte pixels (4 x 16 bit)
 }
 
+// The same padded copy for the one layout that matters in practice -- a dense channels-last RGB image of 16-bit
+// values (pixel pitch 3 elements) -> 4-channel pixels: a thread turns four source pixels (24 bytes, three 8-byte
+// loads) into four destination pixels (32 bytes, four 8-byte stores), and the threads past the image's width write
+// the zero pixels in front of and behind the row. One block per image row. `src_row` / `src_img`: element pitches.
+__global__ void rgb16_rows_to_padded4_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int H, int W,
+                                             int Wp, int pad, long long src_img, long long src_row) {
+  const long long row = blockIdx.x;                       // n * H + h
+  const long long n = row / H, h = row - n * H;
+  const uint2* __restrict__ s = reinterpret_cast<const uint2*>(src + n * src_img + h * src_row);
+  uint2* __restrict__ d = reinterpret_cast<uint2*>(dst + row * Wp * 4);
+  const int groups = W >> 2;
+  for (int t = threadIdx.x; t < groups; t += blockDim.x) {
+    const uint2 a = s[3 * t], b = s[3 * t + 1], c = s[3 * t + 2];   // words w0..w5 = elements e0..e11, two per word
+    uint2* o = d + pad + 4 * t;
+    o[0] = make_uint2(a.x, a.y & 0xffffu);
+    o[1] = make_uint2((a.y >> 16) | (b.x << 16), b.x >> 16);
+    o[2] = make_uint2(b.y, c.x & 0xffffu);
+    o[3] = make_uint2((c.x >> 16) | (c.y << 16), c.y >> 16);
+  }
+  const int zeros = Wp - W;                               // pad in front, the rest behind
+  for (int z = threadIdx.x; z < zeros; z += blockDim.x) d[z < pad ? z : W + z] = make_uint2(0u, 0u);
+}
+
 // w[k, c, r, s] (element strides) -> dst[k][r][s][Cp], zero-padded channels: the K-major B operand
 // whose Kgemm axis runs (r, s, c), the order the reference walks it (conv.rs:209-210).
 // `Sd` >= S is the number of tap slots per filter row in the destination (slots s >= S are zero).

@@ -665,7 +665,14 @@ bool try_row_band_conv(DeviceState& st, Staging&& staging, const View4& x, const
   {
     const int threads = 256;
     const unsigned blocks = static_cast<unsigned>((pixels + threads - 1) / threads);
-    if (Cw == 4)
+    const bool dense_rgb = C == 3 && x.stride[1] == 1 && x.stride[3] == 3 && (W % 4) == 0 && (x.stride[2] % 4) == 0 &&
+                           (x.stride[0] % 4) == 0 && (reinterpret_cast<uintptr_t>(x.ptr) % 8) == 0 &&
+                           N * H <= 0x7fffffffLL;
+    if (dense_rgb)
+      tb200::rgb16_rows_to_padded4_kernel<<<static_cast<unsigned>(N * H), 64, 0, stream>>>(
+          static_cast<const uint16_t*>(x.ptr), static_cast<uint16_t*>(x_stage), (int)H, (int)W, (int)Wpitch,
+          (int)p.padding_w, x.stride[0], x.stride[2]);
+    else if (Cw == 4)
       tb200::to_channels_last_wpad_kernel<uint16_t, 4><<<blocks, threads, 0, stream>>>(
           static_cast<const uint16_t*>(x.ptr), static_cast<uint16_t*>(x_stage), (int)C, (int)H, (int)W, (int)Wpitch,
           (int)p.padding_w, pixels, x.stride[0], x.stride[1], x.stride[2], x.stride[3]);
