@@ -38,6 +38,7 @@ namespace tb200 {
 constexpr int kBlockM = 128;          // output pixels per tile = TMEM lanes
 constexpr int kStageKBytes = 128;     // bytes of K per smem row per pipeline stage
 constexpr int kNumThreads = 320;      // warp 0 TMA, warp 1 MMA, warps 2..5 and 6..9 two epilogue groups
+constexpr int kNumThreadsRows2 = 352; // 256-row tiles of one CTA: warp 10 is a second MMA issuer (the tile's second block)
 constexpr int kMaxStages = 12;
 constexpr long long kWaitLimitCycles = 4000000000LL;  // default limit of one wait: ~2 s at 1.9 GHz (ConvKernelArgs::wait_limit)
 
@@ -336,8 +337,9 @@ __device__ __noinline__ void epilogue_block_generic(const ConvKernelArgs& args, 
 // 128 pixels of A and its own half of B's rows (no multicast), the leader CTA issues M = 256 MMAs that span both
 // SMs, each CTA drains its own 128 TMEM lanes. Per CTA this halves the B bytes brought in per MMA.
 // kRows2 (single CTA, narrow outputs): the CTA owns a 256 x BN tile as two 128-row blocks with one accumulator
-// each; a stage carries both A blocks and one B, i.e. eight MMAs per barrier probe instead of four, and the two
-// epilogue groups drain the two halves of the same tile instead of alternate tiles.
+// each; a stage carries both A blocks and one B; two warps issue the MMAs, one block each (a single thread issues
+// too slowly for MMAs this narrow), and the two epilogue groups drain the two halves of the same tile instead of
+// alternate tiles.
 // Staging box (32 pixel rows x 128 bytes, SWIZZLE_128B layout: 16-byte chunk c of row r at r*128 + ((c ^ (r & 7)) << 4))
 // <-> global memory, moved by the warp itself for outputs the TMA unit cannot address as one matrix. Lane l handles
 // chunk l & 7 of rows (l >> 3) + 4 i, so each instruction covers four whole 128-byte rows. `row_base` points at the
@@ -619,7 +621,7 @@ __device__ __noinline__ void sk_reduce_many(const ConvKernelArgs& a, uint32_t ta
 // launches that split nothing -- most of them -- carry none of the exchange code: the call to it alone costs the
 // epilogue registers, and a spilled register here goes all the way to L2.
 template <typename OutT, int BN, bool kPair, bool kRows2, bool kCoop, bool kSplit>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kRows2 ? kNumThreadsRows2 : kNumThreads, 1)
 conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ CUtensorMap tmap_w,
                           const __grid_constant__ CUtensorMap tmap_out,
@@ -669,10 +671,10 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_stages; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+      mbar_init(empty_bar(s), kRows2 ? 2 : 1);   // one commit per MMA-issuing warp
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(tfull_bar(b), 1);
+      mbar_init(tfull_bar(b), kRows2 ? 2 : 1);
       // one arrival per epilogue warp that drains the buffer: 4, or 8 when both groups / both CTAs of a pair do
       mbar_init(tempty_bar(b), (kPair || kRows2) ? 8 : 4);
     }
@@ -880,18 +882,22 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         while (clock64() - t0 < 2000000LL) { __nanosleep(1000); }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || (kRows2 && warp == 10)) {
     // ------------------------------------------------------------ MMA issuer
     // One thread. Descriptor low words are precomputed per k-slice; per stage they only move by the
     // stage pitch, so an MMA costs two adds and one instruction here (the tensor pipe needs a new
     // 128 x BN x 32-byte MMA every BN/2 cycles).
+    // kRows2 (BN <= 128): one thread cannot issue that fast -- measured about 90 cycles per MMA in this loop against
+    // the 64 an N = 128 MMA takes -- so the tile's two 128-row blocks have an issuer each (warps 1 and 10): separate
+    // accumulators, the same stages; a stage is released, and a tile handed over, when both have committed.
     if (lane == 0 && leader) {
+      const uint32_t blk = (kRows2 && warp == 10) ? 1u : 0u;
       constexpr bool kTf32 = OutTraits<OutT>::kTf32;
       const uint32_t desc_hi = ((args.a_sbo >> 4) & 0x3FFFu) | (1u << 14) | ((args.swizzle_mode & 7u) << 29);
       uint32_t a_k[4], b_k[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        a_k[k] = ((smem_base + args.a_mma_off[k]) >> 4) | (((args.a_lbo >> 4) & 0x3FFFu) << 16);
+        a_k[k] = ((smem_base + args.a_mma_off[k] + blk * kABlockBytes) >> 4) | (((args.a_lbo >> 4) & 0x3FFFu) << 16);
         b_k[k] = ((smem_base + kABytes + args.b_mma_off[k]) >> 4) | (((args.b_lbo >> 4) & 0x3FFFu) << 16);
       }
       constexpr uint32_t kStageUnits = kStageBytes >> 4;
@@ -920,7 +926,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         TB200_PROF_ADD(prof_wtmem, tw0);
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf) * kAccCols;
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf) * kAccCols + blk * BN;
         for (int it = item.k_begin; it < item.k_end; ++it) {
           const bool first = it == item.k_begin;   // the piece's first MMA overwrites the accumulator
           TB200_PROF_T(tw1);
@@ -935,18 +941,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (n_off == ring_units) { n_off = 0; nfull = full_bar0; nempty = empty_bar0; nphase ^= 1u; }
           tc_fence_after();
           bool next_ready;
-          if constexpr (kRows2) {
-            if (first)
-              next_ready = mma_stage8_probe<kTf32, false>(d_tmem, d_tmem + BN, a_k[0] + s_off, a_k[1] + s_off,
-                                                          a_k[2] + s_off, a_k[3] + s_off, kABlockBytes >> 4,
-                                                          b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off, b_k[3] + s_off,
-                                                          desc_hi, idesc, empty_addr, nfull, nphase);
-            else
-              next_ready = mma_stage8_probe<kTf32, true>(d_tmem, d_tmem + BN, a_k[0] + s_off, a_k[1] + s_off,
-                                                         a_k[2] + s_off, a_k[3] + s_off, kABlockBytes >> 4,
-                                                         b_k[0] + s_off, b_k[1] + s_off, b_k[2] + s_off, b_k[3] + s_off,
-                                                         desc_hi, idesc, empty_addr, nfull, nphase);
-          } else if constexpr (kPair) {
+          if constexpr (kPair) {
             if (first)
               next_ready = mma_stage4_probe_pair<kTf32, false>(d_tmem, a_k[0] + s_off, a_k[1] + s_off, a_k[2] + s_off,
                                                                a_k[3] + s_off, b_k[0] + s_off, b_k[1] + s_off,
@@ -975,9 +970,11 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
           else mma_commit(tfull_bar(buf));
         }
       }
-      TB200_PROF_STORE(2, prof_wfull);
-      TB200_PROF_STORE(3, prof_wtmem);
-      TB200_PROF_STORE(4, clock64() - prof_t0);
+      if (blk == 0u) {
+        TB200_PROF_STORE(2, prof_wfull);
+        TB200_PROF_STORE(3, prof_wtmem);
+        TB200_PROF_STORE(4, clock64() - prof_t0);
+      }
     }
   } else {
     // ------------------------------------------------------------ epilogue warps (2..9)

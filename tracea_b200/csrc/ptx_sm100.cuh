@@ -330,66 +330,6 @@ __device__ __forceinline__ bool mma_stage4_probe(uint32_t tmem_d, uint32_t a0, u
   return ready != 0;
 }
 
-// Stage of a two-row-block tile (256 output pixels in ONE CTA, used for narrow outputs where a 128 x BN
-// tile gives the issuing thread too little tensor work per barrier probe): eight MMAs, the first four on
-// pixels 0..127 into accumulator d0, the last four on pixels 128..255 (A operand `a_half` 16-byte units
-// further on) into accumulator d1, both against the same B.
-template <bool kTf32, bool kFirstAccumulates>
-__device__ __forceinline__ bool mma_stage8_probe(uint32_t d0, uint32_t d1, uint32_t a0, uint32_t a1, uint32_t a2,
-                                                 uint32_t a3, uint32_t a_half, uint32_t b0, uint32_t b1, uint32_t b2,
-                                                 uint32_t b3, uint32_t desc_hi, uint32_t idesc, uint32_t empty_bar,
-                                                 uint32_t next_full_bar, uint32_t next_parity) {
-  uint32_t ready;
-#define TB200_MMA_STAGE8(KIND)                                                                  \
-  asm volatile(                                                                                  \
-      "{\n"                                                                                      \
-      ".reg .pred pn, p0, p1;\n"                                                                 \
-      ".reg .b64 da, db;\n"                                                                      \
-      ".reg .b32 ah;\n"                                                                          \
-      "mbarrier.test_wait.parity.shared::cta.b64 pn, [%15], %16;\n"                              \
-      "setp.ne.b32 p0, %17, 0;\n"                                                                \
-      "setp.eq.b32 p1, 0, 0;\n"                                                                  \
-      "mov.b64 da, {%3, %12};\n"                                                                 \
-      "mov.b64 db, {%8, %12};\n"                                                                 \
-      "tcgen05.mma.cta_group::1.kind::" KIND " [%1], da, db, %13, p0;\n"                         \
-      "add.u32 ah, %3, %7;\n"                                                                    \
-      "mov.b64 da, {ah, %12};\n"                                                                 \
-      "tcgen05.mma.cta_group::1.kind::" KIND " [%2], da, db, %13, p0;\n"                         \
-      "mov.b64 da, {%4, %12};\n"                                                                 \
-      "mov.b64 db, {%9, %12};\n"                                                                 \
-      "tcgen05.mma.cta_group::1.kind::" KIND " [%1], da, db, %13, p1;\n"                         \
-      "add.u32 ah, %4, %7;\n"                                                                    \
-      "mov.b64 da, {ah, %12};\n"                                                                 \
-      "tcgen05.mma.cta_group::1.kind::" KIND " [%2], da, db, %13, p1;\n"                         \
-      "mov.b64 da, {%5, %12};\n"                                                                 \
-      "mov.b64 db, {%10, %12};\n"                                                                \
-      "tcgen05.mma.cta_group::1.kind::" KIND " [%1], da, db, %13, p1;\n"                         \
-      "add.u32 ah, %5, %7;\n"                                                                    \
-      "mov.b64 da, {ah, %12};\n"                                                                 \
-      "tcgen05.mma.cta_group::1.kind::" KIND " [%2], da, db, %13, p1;\n"                         \
-      "mov.b64 da, {%6, %12};\n"                                                                 \
-      "mov.b64 db, {%11, %12};\n"                                                                \
-      "tcgen05.mma.cta_group::1.kind::" KIND " [%1], da, db, %13, p1;\n"                         \
-      "add.u32 ah, %6, %7;\n"                                                                    \
-      "mov.b64 da, {ah, %12};\n"                                                                 \
-      "tcgen05.mma.cta_group::1.kind::" KIND " [%2], da, db, %13, p1;\n"                         \
-      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%14];\n"           \
-      "selp.u32 %0, 1, 0, pn;\n"                                                                 \
-      "}\n"                                                                                      \
-      : "=r"(ready)                                                                              \
-      : "r"(d0), "r"(d1), "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(a_half), "r"(b0), "r"(b1), "r"(b2),      \
-        "r"(b3), "r"(desc_hi), "r"(idesc), "r"(empty_bar), "r"(next_full_bar), "r"(next_parity),           \
-        "n"(kFirstAccumulates ? 1 : 0)                                                           \
-      : "memory")
-  if constexpr (kTf32) {
-    TB200_MMA_STAGE8("tf32");
-  } else {
-    TB200_MMA_STAGE8("f16");
-  }
-#undef TB200_MMA_STAGE8
-  return ready != 0;
-}
-
 // The same stage for a CTA pair: issued by the leader CTA only; each MMA spans both SMs (M = 256: 128 rows of
 // A and half of B's rows come from each CTA's shared memory at the same offsets) and the commit arrives on
 // the `empty` barrier at the same offset in BOTH CTAs (multicast arrive, mask 0b11).

@@ -398,7 +398,7 @@ void launch_one_variant(DeviceState& st, int dt_idx, int bn_idx, const CUtensorM
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
-  cfg.blockDim = dim3(tb200::kNumThreads);
+  cfg.blockDim = dim3(kRows2 ? tb200::kNumThreadsRows2 : tb200::kNumThreads);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem);
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
