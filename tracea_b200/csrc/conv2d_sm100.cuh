@@ -111,6 +111,7 @@ struct ConvKernelArgs {
   // error reporting: 4 words {code, block, detail, 0}; first error wins
   uint32_t* status;
   long long wait_limit;   // cycles any single wait may take before the role gives up (args.wait_limit unless a test shortens it)
+  int pdl_mode;           // 0: start the next launch, then wait for the previous one; 1 / 2: see the kernel
   int test_producer_stop; // test hook, -1 in normal use: the TMA producer stops issuing after this many stages and
                           // leaves normally, so that the waits downstream of it run out
   long long* prof;        // cycle counters, only written by -DTB200_PROFILE builds
@@ -705,8 +706,17 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
   // programmatic dependent launch it overlaps the tail of the previous kernel on the stream. From here on global
   // memory is read and written: wait for that kernel to finish (a no-op without such a dependency). The next
   // kernel may be scheduled onto SMs as this grid's CTAs leave them; it waits at the same point.
-  griddep_launch_dependents();
-  griddep_wait();
+  // pdl_mode 1 / 2: a chain of launches that do not depend on each other (the phases of a transposed convolution).
+  // Its head waits BEFORE it lets the next launch start; the members after it start without waiting -- whatever
+  // came before the chain is complete by then -- so their CTAs fill the SMs the previous member's last wave leaves
+  // idle, and wait at their very end instead, which keeps the launches completing in stream order.
+  if (args.pdl_mode == 1) {
+    griddep_wait();
+    griddep_launch_dependents();
+  } else {
+    griddep_launch_dependents();
+    if (args.pdl_mode != 2) griddep_wait();
+  }
   TB200_PROF_NOW(13);
 
   const int chunks_per_stage = kStageKBytes / args.chunk_bytes;
@@ -1353,6 +1363,7 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if constexpr (kPair) tmem_dealloc_pair<kTmemCols>(tmem_base);
     else tmem_dealloc<kTmemCols>(tmem_base);
   }
+  if (args.pdl_mode == 2) griddep_wait();   // do not complete before the launch in front of this one has
   TB200_PROF_NOW(15);
 }
 

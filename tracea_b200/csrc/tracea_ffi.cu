@@ -597,6 +597,9 @@ void launch_weight_pack(const void* src, void* dst, int es, long long K, long lo
 // symmetrically; the phases of a transposed convolution do not.
 struct CoreParams : TraceaConv2dParams {
   long long pad_h_hi = 0, pad_w_hi = 0;
+  // Set by callers that issue several launches which do not depend on each other (the phases of a transposed
+  // convolution): *chain is 0 until one of them has been launched as the head of a chain (see ConvKernelArgs::pdl_mode).
+  int* chain = nullptr;
   CoreParams() : TraceaConv2dParams() {}
   CoreParams(const TraceaConv2dParams& p) : TraceaConv2dParams(p), pad_h_hi(p.padding_h), pad_w_hi(p.padding_w) {}
 };
@@ -962,7 +965,9 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
                  const View4* residual, const View4& out, const CoreParams& p, const Epilogue& epi) {
   cudaStream_t stream = static_cast<cudaStream_t>(p.stream);
   // staging comes from the stream-ordered pool, or from the static scratch for the no-alloc entry
+  bool staged = false;   // this call launches layout adapters in front of its conv kernel
   auto staging = [&](Scratch& s, size_t bytes, const char* what) -> void* {
+    staged = true;
     if (arena != nullptr) return arena->take(bytes, what);
     s.alloc(st, bytes, stream);
     return s.ptr;
@@ -1283,6 +1288,12 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
     const long long lim = g_test_wait_limit.load(std::memory_order_relaxed);
     a.wait_limit = lim > 0 ? lim : tb200::kWaitLimitCycles;
     a.test_producer_stop = g_test_producer_stop.load(std::memory_order_relaxed);
+  }
+  if (p.chain != nullptr && knobs().pdl != 0) {
+    // the head of a chain waits before it lets its successor start; a later member starts without waiting, unless
+    // an adapter kernel of its own sits between it and the member before it
+    if (*p.chain == 0) { a.pdl_mode = 1; *p.chain = 1; }
+    else a.pdl_mode = staged ? 0 : 2;
   }
   // channel-contiguous output (and residual, if any) that the TMA unit cannot address as one matrix: the kernel
   // variant whose epilogue writes its staging boxes out itself, whole 128-byte rows at a time
@@ -1766,6 +1777,7 @@ void conv_transpose_phases(int dev, const View4& x, const View4& w, const View4*
   const long long Ho = out.shape[2], Wo = out.shape[3];
   const long long sh = tp.stride_h, sw = tp.stride_w;
   void* zero_ptr = nullptr;
+  int chain = 0;   // the phases write disjoint outputs and read the same inputs: a chain of independent launches
   for (long long ah = 0; ah < sh; ++ah) {
     for (long long aw = 0; aw < sw; ++aw) {
       PhaseAxis ph = phase_axis(H, Ho, R, sh, tp.padding_h, ah);
@@ -1817,6 +1829,7 @@ void conv_transpose_phases(int dev, const View4& x, const View4& w, const View4*
       cp.padding_w = static_cast<uint32_t>(pw.pad_lo);
       cp.pad_h_hi = ph.pad_hi;
       cp.pad_w_hi = pw.pad_hi;
+      cp.chain = &chain;
       conv2d_device(dev, xp, wp, bias, res != nullptr ? &rp : nullptr, op, cp, epi);
     }
   }
