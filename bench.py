@@ -588,9 +588,11 @@ def time_configs(dev, stream, lib, peaks):
     laid out as the configuration states them (configuration 1 and 2: NCHW activations and OIHW weights, so the
     layout adapters run inside every call and are part of the time), plus the reference's own benchmark layer
     (3x3 64->64 at 56x56, examples/resnet_bench.rs:28-47) at its batch sizes. Device time: CUDA events around
-    `iters` back-to-back calls over rotating operand sets; host time: wall clock per call of issuing them."""
+    `iters` back-to-back calls over rotating operand sets; host time: wall clock per call of issuing them (the
+    argument structs are built once outside the loop, so this is the C entry point's own cost plus the ctypes call)."""
+    import ctypes
     import torch
-    from tracea_b200 import ops
+    from tracea_b200 import ffi, ops
     dt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 
     def one(name, n, c, h, k, r, stride, pad, dtype, epilogue, nchw, iters, sets=3, peak_tf=None):
@@ -602,7 +604,17 @@ def time_configs(dev, stream, lib, peaks):
         kind = ops.parse_epilogue(epilogue or None, bias, None)
         xs = [cl(torch.randn((n, c, h, h), device=dev, generator=g).to(dt[dtype])) for _ in range(sets)]
         outs = [cl(torch.empty((n, k, ho, ho), device=dev, dtype=dt[dtype])) for _ in range(sets)]
-        call = lambda i: ops.conv2d_into(xs[i % sets], w, outs[i % sets], bias, None, stride, pad, 1, 1, kind)
+        # arguments marshalled once, as a C caller of the ABI would hold them: the timed loop is the C entry point alone
+        vw, vb = ops._view(w), (ops._view(bias) if bias is not None else None)
+        views = [(ops._view(xs[i]), ops._view(outs[i])) for i in range(sets)]
+        params = ffi.Conv2dParams(stride, stride, pad, pad, 1, 1, 1, int(kind), ctypes.c_void_p(stream.cuda_stream))
+
+        def call(i):
+            vx, vo = views[i % sets]
+            st = lib.tracea_conv2d(vx.c, vw.c, ctypes.byref(vb.c) if vb is not None else None, None, ctypes.byref(vo.c),
+                                   params)
+            if st != ffi.SUCCESS:
+                raise ffi.TraceaError(st, ffi.last_error())
         for i in range(5):
             call(i)
         torch.cuda.synchronize(dev)
