@@ -538,7 +538,8 @@ dev = lambda a: cl(torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).
 # single CTAs), and fewer tiles than SMs (three and more pieces per tile, two-row-block tiles)
 CASES = [(256, 256, 14, 256, 3, 1, "bias+relu"), (200, 1024, 14, 256, 1, 0, "bias+residual+relu"),
          (64, 512, 7, 512, 3, 1, "bias+relu"), (16, 2048, 7, 512, 1, 0, "bias+silu"), (40, 512, 14, 128, 3, 1, "relu"),
-         (150, 256, 14, 1024, 1, 0, "bias+residual+relu"), (3, 64, 56, 64, 3, 1, "bias+relu")]
+         (150, 256, 14, 1024, 1, 0, "bias+residual+relu"), (3, 64, 56, 64, 3, 1, "bias+relu"),
+         (8, 256, 56, 64, 3, 1, "bias+residual+relu")]   # two-row-block tiles cut in two or three: both groups finish a tile
 for N, C, H, K, R, pad, epi in CASES:
     x = np.abs(cc.normal((N, C, H, H), 3, "sk/x")); w = cc.kaiming((K, C, R, R), 3, "sk/w")
     b = cc.normal((K,), 3, "sk/b", 0.05); r = cc.normal((N, K, H, H), 3, "sk/r")

@@ -1198,8 +1198,9 @@ conv2d_igemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x,
       };
       if constexpr (kSplit) {
         // a piece whose partial sums went to another CTA is finished; one that collected the others' is a whole tile
-        // now (for the group that collected them: a piece is never shared between the groups)
-        if (partial && (((sk_reduced >> local_tile) & 1u) == 0u || (local_tile & 1) != egroup)) continue;
+        // now (for the group that collected them: a piece is never shared between the groups, except that both
+        // groups drain their own row block of a two-row-block tile)
+        if (partial && (((sk_reduced >> local_tile) & 1u) == 0u || (!kRows2 && (local_tile & 1) != egroup))) continue;
       }
       if (!partial) request_first_residual();
 

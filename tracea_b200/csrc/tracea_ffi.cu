@@ -1416,6 +1416,9 @@ void conv2d_core(DeviceState& st, StaticArena* arena, const View4& x_in, const V
               la.dp_tiles = static_cast<int>(tiles - rem);
               la.sk_workers = static_cast<int>(sk_workers);
               workers = tiles >= workers_max ? workers_max : sk_workers;
+              // the exchange scratch belongs to the stream: a launch that uses it must not run beside the launch in
+              // front of it, which may be using it too
+              if (la.pdl_mode == 2) la.pdl_mode = 0;
             }
           }
         }
