@@ -677,3 +677,35 @@ def test_row_band_kernel_agrees_with_the_general_kernel_on_a_zero_padded_image()
     torch.cuda.synchronize()
     a, g = band.float(), general.float()
     assert float((a - g).abs().max()) <= 2.0 ** -7 * float(g.abs().max())
+
+
+def test_row_band_kernel_random_cases():
+    """Seeded random few-channel layers around the row-band kernel's conditions (channels, filter widths up to four
+    K slices, vertical stride / dilation, paddings larger and smaller than the filter needs, ragged column tiles,
+    K_out below 64, both memory layouts): parity with the oracle, and most of them must have taken that kernel."""
+    rng = np.random.default_rng(77)
+    took = 0
+    total = 40
+    for i in range(total):
+        C = int(rng.integers(1, 9))
+        sw = 2 if C <= 4 else 1
+        S = int(rng.integers(2, 9 if C > 4 else 13))
+        R = int(rng.integers(1, 8))
+        sh, dh = int(rng.integers(1, 4)), int(rng.integers(1, 3))
+        W = int(rng.integers(80, 420)) * (2 if sw == 2 else 1)
+        H = int(rng.integers((R - 1) * dh + 1, (R - 1) * dh + 40))
+        K = int(rng.integers(1, 9)) * 8
+        ph, pw = int(rng.integers(0, R + 1)), int(rng.integers(0, S + 2))
+        N = int(rng.integers(1, 4))
+        dtype = str(rng.choice(["bf16", "f16"]))
+        epi = str(rng.choice(["", "bias", "bias+relu", "silu", "bias+gelu".replace("bias+gelu", "gelu")]))
+        cl = bool(rng.integers(0, 2))
+        if (W + 2 * pw - S) // sw + 1 < 1 or (H + 2 * ph - dh * (R - 1) - 1) // sh + 1 < 1:
+            continue
+        x = cc.normal((N, C, H, W), 100 + i, "rbf/x")
+        w = cc.kaiming((K, C, R, S), 100 + i, "rbf/w")
+        b = cc.normal((K,), 100 + i, "rbf/b", 0.1)
+        before = ffi.launch_count_of(ffi.KERNEL_ROW_BAND)
+        check(x, w, b, None, (sh, sw), (ph, pw), (dh, 1), epi, dtype, channels_last=cl, out_channels_last=True)
+        took += ffi.launch_count_of(ffi.KERNEL_ROW_BAND) - before
+    assert took >= total // 2, took
