@@ -250,3 +250,61 @@ def test_nn_module_is_a_drop_in_for_conv2d(cfg):
     assert cc.rel_err(host(y1), cc.round_to(want, "bf16")) <= cc.TOL_16BIT
     with pytest.raises(NotImplementedError):
         tnn.TraceaConv2d(8, 8, 3, groups=2).cuda()(torch.randn(1, 8, 5, 5, device="cuda"))
+
+
+def test_conv_transpose_phases_overlap_and_replay_from_a_cuda_graph():
+    """The phase launches of a transposed convolution do not depend on each other and are issued as a chain of
+    programmatic launches that may run side by side (the first waits before it lets the next one start, the later
+    ones wait at their end). Many waves per phase, a residual, back-to-back calls into the same output, and the same
+    call captured into a CUDA graph and replayed: always the bits of a run with the overlap switched off."""
+    import subprocess
+    import sys
+    rng = np.random.default_rng(5)
+    x = torch.from_numpy(rng.standard_normal((48, 32, 32, 128)).astype(np.float32)).to(torch.bfloat16).cuda()
+    w = torch.from_numpy((rng.standard_normal((128, 4, 4, 128)) * 0.02).astype(np.float32)).to(torch.bfloat16).cuda()
+    b = torch.from_numpy(rng.standard_normal(128).astype(np.float32) * 0.1).cuda()
+    r = torch.from_numpy(rng.standard_normal((48, 64, 64, 128)).astype(np.float32)).to(torch.bfloat16).cuda()
+    run = lambda: ops.conv_transpose2d(x, w, b, r, "bias+residual+relu", stride=2, padding=1)
+    first = run()
+    for _ in range(5):
+        again = run()
+    torch.cuda.synchronize()
+    assert torch.equal(first, again)
+    f32 = lambda t: t.float().cpu().numpy()
+    want = oracle.conv_transpose2d(f32(x[:3]), f32(w), b.cpu().numpy(), f32(r[:3]), 2, 1, 0, "relu")   # three images
+    assert cc.rel_err(f32(first[:3]), cc.round_to(np.ascontiguousarray(want), "bf16")) <= cc.TOL_16BIT
+    # captured and replayed
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run()                                  # warm on the capture stream
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            captured = run()
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        captured.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(captured, first)
+    # the same call with the overlap switched off, in a child process (the switch is read once per process)
+    script = (
+        "import sys, numpy as np, torch\n"
+        "sys.path.insert(0, sys.argv[1])\n"
+        "from tracea_b200 import ops\n"
+        "rng = np.random.default_rng(5)\n"
+        "x = torch.from_numpy(rng.standard_normal((48, 32, 32, 128)).astype(np.float32)).to(torch.bfloat16).cuda()\n"
+        "w = torch.from_numpy((rng.standard_normal((128, 4, 4, 128)) * 0.02).astype(np.float32)).to(torch.bfloat16).cuda()\n"
+        "b = torch.from_numpy(rng.standard_normal(128).astype(np.float32) * 0.1).cuda()\n"
+        "r = torch.from_numpy(rng.standard_normal((48, 64, 64, 128)).astype(np.float32)).to(torch.bfloat16).cuda()\n"
+        "o = ops.conv_transpose2d(x, w, b, r, 'bias+residual+relu', stride=2, padding=1)\n"
+        "torch.cuda.synchronize()\n"
+        "np.save(sys.argv[2], o.view(torch.int16).cpu().numpy())\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(os.environ.get("TMPDIR", "/tmp"), "tb200_ct_serial_%d.npy" % os.getpid())
+    res = subprocess.run([sys.executable, "-c", script, root, path], env=dict(os.environ, TRACEA_B200_PDL="0"),
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    serial = np.load(path)
+    os.remove(path)
+    assert np.array_equal(serial, first.view(torch.int16).cpu().numpy())

@@ -24,7 +24,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "conv2d_sm100.cuh"
-#include "conv2d_window_sm100.cuh"
 
 namespace tb200 {
 
