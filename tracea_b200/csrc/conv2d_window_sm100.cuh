@@ -286,6 +286,32 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
     return t;
   };
 
+  // The pair's own sequence of pair-tiles, the same for every role: its full tiles (pair, pair + num_pairs, ...), then
+  // its short ones. Short tiles are dealt so that they even the load out: when the full tiles do not divide by the
+  // number of pairs, pairs [0, heavy) hold one full tile more than the others, and the others are given short tiles
+  // first, up to the `catch_up` of them that weigh as much as one full tile; the rest go round robin over all pairs.
+  // (Dealt round robin from where the full tiles ended, the busiest pair of the 256-image layer had 46 blocks
+  // against a mean of 43.2; now 44.) Returns the index in the numbering tile_of() takes, -1 past the end.
+  const int pf_tiles = args.pair_tiles_full, ps_tiles = args.pair_tiles - args.pair_tiles_full;
+  const int my_fulls = pair < pf_tiles ? (pf_tiles - pair + num_pairs - 1) / num_pairs : 0;
+  const int heavy = pf_tiles % num_pairs;
+  const int light = num_pairs - heavy;
+  const int catch_up = heavy == 0 || args.nblk_short <= 0 ? 0 : args.nblk_full / args.nblk_short;
+  const int first_deal = min(ps_tiles, light * catch_up);            // short tiles that go to the light pairs only
+  const int my_first = pair >= heavy && first_deal > pair - heavy ? (first_deal - (pair - heavy) + light - 1) / light : 0;
+  auto my_pair_tile = [&](uint32_t it) -> int {
+    const int i = static_cast<int>(it);
+    if (i < my_fulls) return pair + i * num_pairs;
+    int k = i - my_fulls, s;
+    if (k < my_first) {
+      s = (pair - heavy) + k * light;
+    } else {
+      k -= my_first;
+      s = first_deal + pair + k * num_pairs;
+    }
+    return s < ps_tiles ? pf_tiles + s : -1;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread per CTA)
     if (lane == 0) {
@@ -297,7 +323,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
                          static_cast<int>(cta_rank) * 32);
       uint32_t it = 0;
       bool ok = true;
-      for (int j = pair; j < args.pair_tiles && ok; j += num_pairs, ++it) {
+      for (int j; ok && (j = my_pair_tile(it)) >= 0; ++it) {
         if (static_cast<int>(it) == args.test_producer_stop) break;   // test hook: go silent, leave normally
         const uint32_t slot = it & 1u, use = it >> 1;
         if (!mbar_wait_bounded(win_empty(slot), (use & 1u) ^ 1u, abort_p, args.wait_limit)) {
@@ -338,7 +364,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
       const uint32_t row_units = static_cast<uint32_t>(args.Wp) * 8u;          // one window row, in 16-byte units
       const uint32_t idesc = args.idesc;
       const bool three_by_three = args.R == 3 && args.S == 3;
-      for (int j = pair; j < args.pair_tiles && ok; j += num_pairs, ++it) {
+      for (int j; ok && (j = my_pair_tile(it)) >= 0; ++it) {
         const uint32_t slot = it & 1u, use = it >> 1;   // window slot and accumulator buffer alternate together
         const int nblk = j < args.pair_tiles_full ? args.nblk_full : args.nblk_short;
         TB200_PROF_T(tw0);
@@ -407,7 +433,7 @@ conv2d_window_sm100_kernel(const __grid_constant__ CUtensorMap tmap_x_full,
     long long prof_wacc = 0;
     (void)prof_wacc;
     TB200_PROF_T(prof_t0);
-    for (int j = pair; j < args.pair_tiles && ok; j += num_pairs, ++it) {
+    for (int j; ok && (j = my_pair_tile(it)) >= 0; ++it) {
       const uint32_t buf = it & 1u, use = it >> 1;
       const Tile t = tile_of(j);
       TB200_PROF_T(tw2);
